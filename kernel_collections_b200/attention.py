@@ -1,0 +1,192 @@
+"""Drop-in equivalents of the reference's eager decode functions (attention.py there).
+
+Same names, argument order, shapes and return values; the work runs in libxkv's CUDA
+kernels.  All functions are single decode steps (q_len == 1).  `attn_mask` and `dropout_p`
+are accepted for signature compatibility; anything but None / 0.0 raises
+NotImplementedError (there is no CPU or eager fallback).
+
+Keyword-only extras, defaulting to the reference's behaviour: `sm_scale` (multiplies the
+logits), `theta`, `k_position_offset` (RoPE position of key row 0).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _C, ops
+
+
+def _no_mask(attn_mask, dropout_p):
+    if attn_mask is not None or dropout_p != 0.0:
+        raise NotImplementedError("attn_mask / dropout are not supported by the decode kernels")
+
+
+def _q3(query):
+    if query.dim() != 4:
+        raise ValueError(f"query must be (bsz, num_heads, 1, head_dim); got {tuple(query.shape)}")
+    if query.shape[2] != 1:
+        raise AssertionError("q_len must be 1")
+    return query[:, :, 0, :]
+
+
+def group_query_attention(query, key, value, attn_mask=None, dropout_p=0.0, *, sm_scale=None):
+    """Dense GQA decode.  Reference: attention.py:7-90.
+
+    query (bsz, num_heads, 1, head_dim); key/value (bsz, num_kv_heads, kv_len, head_dim)
+    -> (bsz, num_heads, 1, head_dim).  Logits are divided by sqrt(head_dim) as there."""
+    _no_mask(attn_mask, dropout_p)
+    bsz, num_heads, _, head_dim = query.shape
+    if key.shape[0] != bsz or value.shape[0] != bsz:
+        raise AssertionError("Batch size mismatch among Q, K, V.")
+    if key.shape[1] != value.shape[1]:
+        raise AssertionError("num_kv_heads mismatch between K, V.")
+    if key.shape[3] != head_dim or value.shape[3] != head_dim:
+        raise AssertionError("head_dim mismatch among Q, K, V.")
+    if key.shape[2] != value.shape[2]:
+        raise AssertionError("kv_len mismatch between K, V.")
+    if num_heads % key.shape[1] != 0:
+        raise AssertionError("num_heads must be multiple of num_kv_heads.")
+    scale = head_dim ** -0.5 if sm_scale is None else sm_scale
+    o = ops.decode(entry="xkv_dense_decode", score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE,
+                   q=_q3(query), k=key.transpose(1, 2), v=value.transpose(1, 2), sm_scale=scale)
+    return o.unsqueeze(2)
+
+
+def group_query_attention_fa(query, key, value, attn_mask=None, dropout_p=0.0):
+    """Flash-decoding layout of the same op.  Reference: attention.py:184-191, which forwards to
+    flash_attn_with_kvcache(q, k, v, causal=True): query (bsz, 1, num_heads, head_dim),
+    key/value (bsz, kv_len, num_kv_heads, head_dim) -> (bsz, 1, num_heads, head_dim); the
+    softmax scale is 1/sqrt(head_dim) and, with one query token, causal means "attend to all".
+    The mask / dropout arguments are ignored there and here."""
+    if query.dim() != 4 or query.shape[1] != 1:
+        raise ValueError(f"query must be (bsz, 1, num_heads, head_dim); got {tuple(query.shape)}")
+    o = ops.decode(entry="xkv_dense_decode", score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE,
+                   q=query[:, 0], k=key, v=value, sm_scale=query.shape[-1] ** -0.5)
+    return o.unsqueeze(1)
+
+
+def group_query_attention_factorized_v_only(query, key, value_A, value_B, attn_mask=None, dropout_p=0.0):
+    """Dense K, V = value_A @ value_B.  Reference: attention.py:202-274.
+
+    key (bsz, num_kv_heads, kv_len, head_dim); value_A (bsz, kv_len, v_rank);
+    value_B (bsz, num_kv_heads, v_rank, head_dim)."""
+    _no_mask(attn_mask, dropout_p)
+    if value_A.shape[-1] != value_B.shape[2]:
+        raise AssertionError("Rank mismatch between value_A and value_B")
+    if query.shape[1] % key.shape[1] != 0:
+        raise AssertionError("num_heads must be divisible by num_kv_heads")
+    o = ops.decode(entry="xkv_absorbed_decode", score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_LATENT,
+                   q=_q3(query), k=key.transpose(1, 2), v=value_A, v_proj=value_B,
+                   sm_scale=query.shape[-1] ** -0.5)
+    return o.unsqueeze(2)
+
+
+def group_query_attention_factorized(query, key_A, key_B, value_A, value_B, attn_mask=None,
+                                     dropout_p=0.0, *, sm_scale=None):
+    """K = key_A @ key_B, V = value_A @ value_B in absorbed form.  Reference: attention.py:276-357.
+
+    key_A (bsz, kv_len, k_rank); key_B (bsz, num_kv_heads, k_rank, head_dim); value_A / value_B
+    alike.  Logits are divided by sqrt(head_dim)."""
+    _no_mask(attn_mask, dropout_p)
+    if key_A.shape[-1] != key_B.shape[2]:
+        raise AssertionError("Rank mismatch between key_A and key_B")
+    if value_A.shape[-1] != value_B.shape[2]:
+        raise AssertionError("Rank mismatch between value_A and value_B")
+    if query.shape[1] % key_B.shape[1] != 0:
+        raise AssertionError("num_heads must be divisible by num_kv_heads")
+    scale = query.shape[-1] ** -0.5 if sm_scale is None else sm_scale
+    o = ops.decode(entry="xkv_absorbed_decode", score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT,
+                   q=_q3(query), k=key_A, k_proj=key_B, v=value_A, v_proj=value_B, sm_scale=scale)
+    return o.unsqueeze(2)
+
+
+def group_query_attention_factorized_RoPE(query, key_A, key_B, value_A, value_B, attn_mask=None,
+                                          dropout_p=0.0, *, theta=10000000.0, sm_scale=1.0,
+                                          k_position_offset=0):
+    """Factorized K with RoPE applied to the rebuilt keys, factorized V.  Reference:
+    attention.py:360-431 — logits q . RoPE_l(key_A[l] @ key_B) with theta 1e7 and NO 1/sqrt(d)
+    scaling (:393-396), key position = row index, q used as given."""
+    _no_mask(attn_mask, dropout_p)
+    if key_A.shape[-1] != key_B.shape[2]:
+        raise AssertionError("Rank mismatch between key_A and key_B")
+    if value_A.shape[-1] != value_B.shape[2]:
+        raise AssertionError("Rank mismatch between value_A and value_B")
+    o = ops.decode(entry="xkv_recon_rope_decode", score_mode=_C.SCORE_RECON_ROPE,
+                   value_mode=_C.VALUE_LATENT, q=_q3(query), k=key_A, k_proj=key_B, v=value_A,
+                   v_proj=value_B, sm_scale=sm_scale, theta=theta, pos_offset=k_position_offset)
+    return o.unsqueeze(2)
+
+
+# ---- entry points the reference does not have but its benchmark configurations need -------------
+def recon_rope_decode(query, key_A, key_B, value, value_B=None, *, theta, sm_scale=None,
+                      k_position_offset=0, num_splits=0, force_generic=False):
+    """Factorized K + RoPE with dense V (bsz, num_kv_heads, kv_len, head_dim), or factorized V
+    when value_B is given (then `value` is the value latent).  key_B may be (bsz|1, num_kv_heads,
+    k_rank, head_dim) or a shared (k_rank, num_kv_heads*head_dim) matrix.  Default scale
+    1/sqrt(head_dim).  Per call this is attention.py:7-90 on K = RoPE(A.B)."""
+    q = _q3(query)
+    D = q.shape[-1]
+    key_B = as_key_proj(key_B, D)
+    scale = D ** -0.5 if sm_scale is None else sm_scale
+    kw = dict(score_mode=_C.SCORE_RECON_ROPE, q=q, k=key_A, k_proj=key_B, sm_scale=scale, theta=theta,
+              pos_offset=k_position_offset, num_splits=num_splits, force_generic=force_generic)
+    if value_B is None:
+        o = ops.decode(entry="xkv_recon_rope_decode", value_mode=_C.VALUE_DENSE, v=value.transpose(1, 2), **kw)
+    else:
+        o = ops.decode(entry="xkv_recon_rope_decode", value_mode=_C.VALUE_LATENT, v=value,
+                       v_proj=as_key_proj(value_B, D), **kw)
+    return o.unsqueeze(2)
+
+
+def as_key_proj(B, head_dim):
+    """Accept the per-batch (bsz, KVH, R, D) form or a shared (R, KVH*D) matrix."""
+    if B.dim() == 2:
+        R = B.shape[0]
+        return B.view(R, -1, head_dim).permute(1, 0, 2).unsqueeze(0)
+    return B
+
+
+def rope_query(query, theta, position):
+    """Rotate a decode-step query (bsz, num_heads, 1, head_dim) to `position` (half-split RoPE,
+    flash_recontruction/rope/rope_ref.py:11-21).  Tiny; done with torch ops on the device."""
+    D = query.shape[-1]
+    f = _C.inv_freq(D, theta, query.device)
+    ang = torch.tensor(float(position), dtype=torch.float32, device=query.device) * f
+    cos = torch.cat((ang, ang)).cos()
+    sin = torch.cat((ang, ang)).sin()
+    x = query.float()
+    h = D // 2
+    rot = torch.cat((-x[..., h:], x[..., :h]), dim=-1)
+    return (x * cos + rot * sin).to(query.dtype)
+
+
+def xkv_group_decode(queries, key_A, key_Bs, value, value_Bs=None, *, theta, sm_scale=None,
+                     k_position_offset=0):
+    """Cross-layer group: NL layers share key_A (and the value latent when value_Bs is given).
+
+    queries: sequence of (bsz, H, 1, D); key_Bs: per-layer key projections; value: the shared
+    value latent (bsz, L, Rv) with value_Bs, or a per-layer sequence of dense V
+    (bsz, KVH, L, D).  Returns a list of (bsz, H, 1, D)."""
+    D = queries[0].shape[-1]
+    scale = D ** -0.5 if sm_scale is None else sm_scale
+    layers = []
+    for i, q in enumerate(queries):
+        kw = dict(score_mode=_C.SCORE_RECON_ROPE, q=_q3(q), k=key_A, k_proj=as_key_proj(key_Bs[i], D),
+                  sm_scale=scale, theta=theta, pos_offset=k_position_offset)
+        if value_Bs is None:
+            kw.update(value_mode=_C.VALUE_DENSE, v=value[i].transpose(1, 2))
+        else:
+            kw.update(value_mode=_C.VALUE_LATENT, v=value, v_proj=as_key_proj(value_Bs[i], D))
+        layers.append(kw)
+    return [o.unsqueeze(2) for o in ops.group_decode(layers)]
+
+
+def mla_absorbed_decode(q_nope, q_rope, c_kv, k_rope, W_uk, W_uv, sm_scale):
+    """MLA absorbed decode.  q_nope (b,H,nope); q_rope (b,H,rope); c_kv (b,L,lora);
+    k_rope (b,L,rope); W_uk (H,nope,lora); W_uv (H,lora,v) -> (b,H,v).  W_uk is folded into q,
+    the latent is streamed once for both logits and values, W_uv is applied after the merge.
+    The attention core is flash_decoding/mla2/mla_flash_decoding.py:6-62."""
+    kp = W_uk.permute(0, 2, 1).unsqueeze(0)      # (1, H, lora, nope): element [h, r, d] = W_uk[h, d, r]
+    vp = W_uv.unsqueeze(0)                       # (1, H, lora, v)
+    return ops.decode(entry="xkv_mla_decode", score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT,
+                      q=q_nope, k=c_kv, k_proj=kp, v=c_kv, v_proj=vp, q_tail=q_rope, k_tail=k_rope,
+                      sm_scale=sm_scale, num_kv_heads=1)

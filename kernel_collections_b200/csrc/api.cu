@@ -1,0 +1,217 @@
+// C ABI of libxkv: parameter validation, kernel selection, named entry points.
+#include "xkv_internal.h"
+#include <string.h>
+
+namespace xkv {
+namespace {
+
+bool is_recon(int m) { return m == XKV_SCORE_RECON || m == XKV_SCORE_RECON_ROPE; }
+
+int validate(const xkv_decode_params* p) {
+  if (!p) return XKV_ERR_BAD_ARG;
+  if (p->dtype < XKV_F32 || p->dtype > XKV_F16) return XKV_ERR_BAD_ARG;
+  if (p->score_mode < XKV_SCORE_DENSE || p->score_mode > XKV_SCORE_RECON) return XKV_ERR_BAD_ARG;
+  if (p->value_mode < XKV_VALUE_DENSE || p->value_mode > XKV_VALUE_LATENT) return XKV_ERR_BAD_ARG;
+  if (p->batch <= 0 || p->num_heads <= 0 || p->num_kv_heads <= 0 || p->kv_len <= 0) return XKV_ERR_BAD_ARG;
+  if (p->head_dim <= 0) return XKV_ERR_BAD_ARG;
+  if (p->num_heads % p->num_kv_heads != 0) return XKV_ERR_BAD_ARG;
+  if (p->num_splits < 0) return XKV_ERR_BAD_ARG;
+  if (!p->q || !p->k) return XKV_ERR_BAD_ARG;
+  const bool logits_only = (p->flags & XKV_FLAG_LOGITS_ONLY) != 0;
+  if (p->tail_dim < 0) return XKV_ERR_BAD_ARG;
+  if (p->tail_dim > 0) {
+    if (p->score_mode != XKV_SCORE_LATENT) return XKV_ERR_BAD_ARG;
+    if (!p->q_tail || !p->k_tail) return XKV_ERR_BAD_ARG;
+  }
+  if (p->score_mode != XKV_SCORE_DENSE) {
+    if (p->k_rank <= 0) return XKV_ERR_BAD_ARG;
+    if (is_recon(p->score_mode) && !p->k_proj) return XKV_ERR_BAD_ARG;
+    if (p->k_proj) {
+      if (p->k_proj_heads <= 0 || p->num_heads % p->k_proj_heads != 0) return XKV_ERR_BAD_ARG;
+      if (is_recon(p->score_mode) && p->k_proj_heads != p->num_kv_heads) return XKV_ERR_BAD_ARG;
+    } else if (p->head_dim != p->k_rank) {
+      return XKV_ERR_BAD_ARG;
+    }
+    if (p->score_mode == XKV_SCORE_RECON_ROPE && (p->head_dim & 1)) return XKV_ERR_BAD_ARG;
+  }
+  if (logits_only) {
+    if (!p->logits) return XKV_ERR_BAD_ARG;
+  } else {
+    if (!p->v || !p->out || p->value_dim <= 0) return XKV_ERR_BAD_ARG;
+    if (p->value_mode == XKV_VALUE_LATENT) {
+      if (p->v_rank <= 0) return XKV_ERR_BAD_ARG;
+      if (p->v_proj) {
+        if (p->v_proj_heads <= 0 || p->num_heads % p->v_proj_heads != 0) return XKV_ERR_BAD_ARG;
+      } else if (p->value_dim != p->v_rank) {
+        return XKV_ERR_BAD_ARG;
+      }
+    }
+  }
+  return XKV_OK;
+}
+
+enum class Path { kNone, kGeneric, kReconTc };
+
+Path select(const xkv_decode_params& p, GenericPlan* gp, ReconTcPlan* rp) {
+  if (!(p.flags & XKV_FLAG_FORCE_GENERIC) && recon_tc_supported(p) && recon_tc_plan(p, rp))
+    return Path::kReconTc;
+  if (generic_plan(p, gp)) return Path::kGeneric;
+  return Path::kNone;
+}
+
+int check_mode(const xkv_decode_params* p, bool ok) {
+  if (!p) return XKV_ERR_BAD_ARG;
+  return ok ? XKV_OK : XKV_ERR_BAD_ARG;
+}
+
+}  // namespace
+}  // namespace xkv
+
+using namespace xkv;
+
+extern "C" {
+
+int xkv_version(void) { return XKV_VERSION; }
+
+size_t xkv_decode_params_size(void) { return sizeof(xkv_decode_params); }
+
+const char* xkv_strerror(int status) {
+  switch (status) {
+    case XKV_OK: return "ok";
+    case XKV_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size or inconsistent shapes)";
+    case XKV_ERR_UNSUPPORTED: return "shape outside the limits of the kernels";
+    case XKV_ERR_ALIGN: return "pointer or stride not aligned as the kernel requires";
+    case XKV_ERR_WORKSPACE: return "workspace missing or too small";
+    case XKV_ERR_LAUNCH: return "CUDA launch failed";
+    case XKV_ERR_TIMEOUT: return "bounded device-side wait expired";
+    case XKV_ERR_NO_DEVICE: return "no usable sm_100 device or driver entry point";
+    default: return "unknown status";
+  }
+}
+
+const char* xkv_decode_plan(const xkv_decode_params* p) {
+  if (validate(p) != XKV_OK) return nullptr;
+  GenericPlan gp;
+  ReconTcPlan rp;
+  switch (select(*p, &gp, &rp)) {
+    case Path::kReconTc: return "recon_tc";
+    case Path::kGeneric: return "generic";
+    default: return nullptr;
+  }
+}
+
+size_t xkv_decode_workspace_bytes(const xkv_decode_params* p) {
+  if (validate(p) != XKV_OK) return 0;
+  GenericPlan gp;
+  ReconTcPlan rp;
+  switch (select(*p, &gp, &rp)) {
+    case Path::kReconTc: return rp.total_bytes;
+    case Path::kGeneric: return gp.total_bytes;
+    default: return 0;
+  }
+}
+
+int xkv_decode(const xkv_decode_params* p, void* ws, size_t ws_bytes, void* stream) {
+  int rc = validate(p);
+  if (rc != XKV_OK) return rc;
+  GenericPlan gp;
+  ReconTcPlan rp;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (select(*p, &gp, &rp)) {
+    case Path::kReconTc:
+      if (!ws || ws_bytes < rp.total_bytes) return XKV_ERR_WORKSPACE;
+      return recon_tc_decode(*p, rp, ws, st);
+    case Path::kGeneric:
+      if (!ws || ws_bytes < gp.total_bytes) return XKV_ERR_WORKSPACE;
+      return generic_decode(*p, gp, ws, st);
+    default:
+      return XKV_ERR_UNSUPPORTED;
+  }
+}
+
+int xkv_dense_decode(const xkv_decode_params* p, void* ws, size_t n, void* st) {
+  int rc = check_mode(p, p && p->score_mode == XKV_SCORE_DENSE && p->value_mode == XKV_VALUE_DENSE &&
+                             !(p->flags & XKV_FLAG_LOGITS_ONLY));
+  return rc != XKV_OK ? rc : xkv_decode(p, ws, n, st);
+}
+
+int xkv_absorbed_decode(const xkv_decode_params* p, void* ws, size_t n, void* st) {
+  int rc = check_mode(p, p && !(p->flags & XKV_FLAG_LOGITS_ONLY) && p->tail_dim == 0 &&
+                             (p->score_mode == XKV_SCORE_LATENT || p->score_mode == XKV_SCORE_DENSE) &&
+                             (p->score_mode == XKV_SCORE_LATENT || p->value_mode == XKV_VALUE_LATENT));
+  return rc != XKV_OK ? rc : xkv_decode(p, ws, n, st);
+}
+
+int xkv_recon_rope_decode(const xkv_decode_params* p, void* ws, size_t n, void* st) {
+  int rc = check_mode(p, p && p->score_mode == XKV_SCORE_RECON_ROPE && !(p->flags & XKV_FLAG_LOGITS_ONLY));
+  return rc != XKV_OK ? rc : xkv_decode(p, ws, n, st);
+}
+
+int xkv_qab_logits(const xkv_decode_params* p, void* ws, size_t n, void* st) {
+  int rc = check_mode(p, p && (p->flags & XKV_FLAG_LOGITS_ONLY) && p->score_mode != XKV_SCORE_DENSE);
+  return rc != XKV_OK ? rc : xkv_decode(p, ws, n, st);
+}
+
+int xkv_mla_decode(const xkv_decode_params* p, void* ws, size_t n, void* st) {
+  int rc = check_mode(p, p && p->score_mode == XKV_SCORE_LATENT && p->value_mode == XKV_VALUE_LATENT &&
+                             p->num_kv_heads == 1 && !(p->flags & XKV_FLAG_LOGITS_ONLY));
+  return rc != XKV_OK ? rc : xkv_decode(p, ws, n, st);
+}
+
+// Group decode: the layers share the key latent.  Each layer runs the single-layer path on the
+// shared workspace, back to back on the stream, so the latent tiles of layer i+1 are served
+// from L2 where the group's latent fits.
+static int group_check(const xkv_decode_params* layers, int n) {
+  if (!layers || n <= 0) return XKV_ERR_BAD_ARG;
+  for (int i = 0; i < n; ++i) {
+    int rc = validate(&layers[i]);
+    if (rc != XKV_OK) return rc;
+    const xkv_decode_params &a = layers[0], &b = layers[i];
+    if (a.dtype != b.dtype || a.score_mode != b.score_mode || a.value_mode != b.value_mode ||
+        a.batch != b.batch || a.num_heads != b.num_heads || a.num_kv_heads != b.num_kv_heads ||
+        a.kv_len != b.kv_len || a.head_dim != b.head_dim || a.value_dim != b.value_dim ||
+        a.k_rank != b.k_rank || a.v_rank != b.v_rank || a.tail_dim != b.tail_dim)
+      return XKV_ERR_BAD_ARG;
+    if (a.score_mode != XKV_SCORE_DENSE && a.k != b.k) return XKV_ERR_BAD_ARG;
+    if (a.value_mode == XKV_VALUE_LATENT && a.v != b.v) return XKV_ERR_BAD_ARG;
+  }
+  return XKV_OK;
+}
+
+size_t xkv_group_decode_workspace_bytes(const xkv_decode_params* layers, int n) {
+  if (group_check(layers, n) != XKV_OK) return 0;
+  size_t mx = 0;
+  for (int i = 0; i < n; ++i) {
+    size_t b = xkv_decode_workspace_bytes(&layers[i]);
+    if (b == 0) return 0;
+    if (b > mx) mx = b;
+  }
+  return mx;
+}
+
+int xkv_group_decode(const xkv_decode_params* layers, int n, void* ws, size_t ws_bytes, void* stream) {
+  int rc = group_check(layers, n);
+  if (rc != XKV_OK) return rc;
+  for (int i = 0; i < n; ++i) {
+    rc = xkv_decode(&layers[i], ws, ws_bytes, stream);
+    if (rc != XKV_OK) return rc;
+  }
+  return XKV_OK;
+}
+
+int xkv_merge(const float* partial_o, const float* lse, void* out, int dtype, int batch, int num_heads,
+              int num_splits, int dim, int64_t o_sb, int64_t o_sh, void* stream) {
+  if (!partial_o || !lse || !out || batch <= 0 || num_heads <= 0 || num_splits <= 0 || dim <= 0)
+    return XKV_ERR_BAD_ARG;
+  return launch_merge(partial_o, lse, out, dtype, batch, num_heads, num_splits, dim, dim, nullptr, 1, 0, 0,
+                      0, 0, o_sb, o_sh, static_cast<cudaStream_t>(stream));
+}
+
+int xkv_rope_table(float* cos_sin, int kv_len, int half, int pos_offset, float theta,
+                   const float* inv_freq, void* stream) {
+  if (!cos_sin || kv_len <= 0 || half <= 0) return XKV_ERR_BAD_ARG;
+  return launch_rope_table(cos_sin, kv_len, half, pos_offset, theta, inv_freq,
+                           static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

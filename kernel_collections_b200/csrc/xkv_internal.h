@@ -1,0 +1,50 @@
+// Internal declarations shared by the translation units of libxkv.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include "xkv.h"
+
+namespace xkv {
+
+constexpr int kNumSMsFallback = 148;
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline int elem_size(int dtype) { return dtype == XKV_F32 ? 4 : 2; }
+
+int device_sm_count();
+
+// ---- portable CUDA-core path (generic_decode.cu) -------------------------------------------
+struct GenericPlan {
+  int heads_per_cta;   // query heads handled by one CTA (divides the GQA group size)
+  int head_chunks;     // num_heads / heads_per_cta
+  int num_splits;      // KV splits
+  int split_len;       // tokens per split (multiple of the token tile)
+  int score_dim;       // width of the (effective) query / key rows
+  int acc_dim;         // width of the accumulated value rows
+  size_t off_qeff, off_partial, off_lse, total_bytes;
+  size_t smem_bytes;
+};
+bool generic_plan(const xkv_decode_params& p, GenericPlan* plan);
+int generic_decode(const xkv_decode_params& p, const GenericPlan& plan, void* ws, cudaStream_t st);
+int launch_merge(const float* partial_o, const float* lse, void* out, int dtype, int batch,
+                 int num_heads, int num_splits, int acc_dim, int value_dim, const void* v_proj,
+                 int v_proj_heads, int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd,
+                 int64_t o_sb, int64_t o_sh, cudaStream_t st);
+int launch_rope_table(float* cos_sin, int kv_len, int half, int pos_offset, float theta,
+                      const float* inv_freq, cudaStream_t st);
+
+// ---- tcgen05 key-reconstruction path (recon_tc_sm100.cu) ------------------------------------
+struct ReconTcPlan {
+  int num_splits;       // CTAs per batch row
+  int tiles_per_split;  // 128-token tiles per CTA
+  size_t off_table, off_partial, off_lse, total_bytes;
+};
+bool recon_tc_supported(const xkv_decode_params& p);
+bool recon_tc_plan(const xkv_decode_params& p, ReconTcPlan* plan);
+int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& plan, void* ws, cudaStream_t st);
+
+}  // namespace xkv

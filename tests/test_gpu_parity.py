@@ -1,0 +1,300 @@
+"""GPU parity: every reference-named entry point (through the C ABI) against the CPU oracle on
+the same seeded inputs.  Primary oracle = eager math in fp32 on the dtype-rounded inputs.
+
+Tolerances: fp32 max-abs and rel-L2 <= 1e-4; bf16 / fp16 max-abs <= 2e-2 and rel-L2 <= 1e-2
+(max-abs is taken relative to max(1, |ref|max) so unscaled logits of magnitude ~10 are judged
+in their own units)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import kernel_collections_b200 as K
+from kernel_collections_b200 import flash_recontruction as FR
+from kernel_collections_b200 import flash_decoding as FD
+from kernel_collections_b200 import _C, ops
+from oracle import xkv_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+def tol(dtype):
+    return (1e-4, 1e-4) if dtype == torch.float32 else (2e-2, 1e-2)
+
+
+def check(got, want, dtype, what=""):
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    assert got.dtype == dtype, (what, got.dtype)
+    assert torch.isfinite(got.float()).all(), f"{what}: non-finite output"
+    max_abs, rel = O.error_metrics(got, want)
+    ta, tr = tol(dtype)
+    scale = max(1.0, want.abs().max().item())
+    assert max_abs <= ta * scale and rel <= tr, f"{what}: max_abs={max_abs:.3e} (scale {scale:.2f}) rel_l2={rel:.3e}"
+
+
+def mk(shape, dtype, scale=1.0, gen=None):
+    """Seeded CPU fp32 normal, rounded to dtype; returns (cpu tensor in dtype, cuda copy)."""
+    x = (torch.randn(shape, generator=gen) * scale).to(dtype)
+    return x, x.to(DEV)
+
+
+def g(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+SHAPES = [  # b, H, KVH, D, L
+    (2, 8, 2, 64, 100),
+    (1, 4, 4, 128, 1),
+    (1, 32, 8, 128, 1000),
+    (3, 7, 1, 32, 17),
+    (2, 16, 2, 16, 16),
+    (1, 6, 2, 80, 333),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", SHAPES)
+def test_dense_gqa(dtype, shape):
+    b, H, KVH, D, L = shape
+    gen = g(1)
+    q, qd = mk((b, H, 1, D), dtype, gen=gen)
+    k, kd = mk((b, KVH, L, D), dtype, gen=gen)
+    v, vd = mk((b, KVH, L, D), dtype, gen=gen)
+    check(K.group_query_attention(qd, kd, vd), O.gqa_dense(q, k, v), dtype, "group_query_attention")
+    # flash layout: (b,1,H,D) / (b,L,KVH,D)
+    out = K.group_query_attention_fa(qd.transpose(1, 2), kd.transpose(1, 2).contiguous(),
+                                     vd.transpose(1, 2).contiguous())
+    check(out.transpose(1, 2), O.gqa_dense(q, k, v), dtype, "group_query_attention_fa")
+    # flash_decoding.gqa with explicit scale and in-place output
+    o = torch.zeros(b, H, D, dtype=dtype, device=DEV)
+    splits = torch.full((b,), 8, dtype=torch.int32, device=DEV)
+    r = FD.gqa.decode_attention_fwd(qd[:, :, 0], kd.transpose(1, 2), vd.transpose(1, 2), o, splits, 8, 0.3)
+    assert r is o
+    check(o, O.flash_decode_gqa(q[:, :, 0], k.transpose(1, 2), v.transpose(1, 2), 0.3), dtype, "gqa.decode_attention_fwd")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(2, 8, 2, 64, 100, 24, 40), (1, 32, 8, 128, 700, 256, 384), (2, 4, 1, 32, 9, 5, 3)])
+def test_factorized_family(dtype, shape):
+    b, H, KVH, D, L, Rk, Rv = shape
+    gen = g(2)
+    q, qd = mk((b, H, 1, D), dtype, gen=gen)
+    k, kd = mk((b, KVH, L, D), dtype, gen=gen)
+    v, vd = mk((b, L, KVH, D), dtype, gen=gen)
+    Ak, Akd = mk((b, L, Rk), dtype, gen=gen)
+    Bk, Bkd = mk((b, KVH, Rk, D), dtype, Rk ** -0.5, gen=gen)
+    Av, Avd = mk((b, L, Rv), dtype, gen=gen)
+    Bv, Bvd = mk((b, KVH, Rv, D), dtype, Rv ** -0.5, gen=gen)
+    check(K.group_query_attention_factorized_v_only(qd, kd, Avd, Bvd),
+          O.gqa_factorized_v_only(q, k, Av, Bv), dtype, "factorized_v_only")
+    check(K.group_query_attention_factorized(qd, Akd, Bkd, Avd, Bvd),
+          O.gqa_factorized(q, Ak, Bk, Av, Bv), dtype, "factorized")
+    check(FR.qAB_no_pe_v1(qd, Akd, Bkd), O.qab_no_pe(q, Ak, Bk), dtype, "qAB_no_pe_v1")
+    check(FR.qAB_no_pe_v2(qd, Akd, Bkd), O.qab_no_pe(q, Ak, Bk), dtype, "qAB_no_pe_v2")
+    # fused xKV entry points, q 3-D, explicit multiply scale
+    q3, q3d = q[:, :, 0], qd[:, :, 0]
+    splits = torch.full((b,), 16, dtype=torch.int32, device=DEV)
+    s = 0.11
+    want = O.xkv_fused(q3, Ak, Bk, Av, Bv, s)
+    o = torch.zeros(b, H, D, dtype=dtype, device=DEV)
+    assert FR.gqa_xKV_no_pe(q3d, Akd, Bkd, Avd, Bvd, o, splits, 16, s) is o
+    check(o, want, dtype, "gqa_xKV_no_pe")
+    check(FR.gqa_xKV_no_pe_v2(q3d, Akd, Bkd, Avd, Bvd, splits, 16, s), want, dtype, "gqa_xKV_no_pe_v2")
+    o2 = torch.zeros(b, H, D, dtype=dtype, device=DEV)
+    FR.gqa_xKV_no_pe_k_only(q3d, Akd, Bkd, vd, o2, splits, 16, s)
+    check(o2, O.xkv_fused_k_only(q3, Ak, Bk, v, s), dtype, "gqa_xKV_no_pe_k_only")
+    s1 = 1.0 if dtype == torch.float32 else None
+    if s1:  # the unscaled *_ref names (scale 1 makes bf16 softmax very peaked; fp32 only)
+        check(FR.gqa_xKV_no_pe_ref(q3d * 0.2, Akd, Bkd, Avd, Bvd), O.xkv_fused(q3 * 0.2, Ak, Bk, Av, Bv, 1.0), dtype, "xKV_ref")
+        check(FR.gqa_xKV_no_pe_k_only_ref(q3d * 0.2, Akd, Bkd, vd), O.xkv_fused_k_only(q3 * 0.2, Ak, Bk, v, 1.0), dtype, "xKV_k_only_ref")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(2, 8, 2, 64, 100, 24, 10000.0), (1, 32, 8, 128, 520, 64, 500000.0),
+                                   (1, 4, 1, 128, 130, 32, 1e7), (2, 4, 4, 16, 5, 3, 10000.0)])
+def test_qab_rope_and_recon_decode(dtype, shape):
+    b, H, KVH, D, L, R, theta = shape
+    gen = g(3)
+    q, qd = mk((b, H, 1, D), dtype, gen=gen)
+    A, Ad = mk((b, L, R), dtype, gen=gen)
+    B, Bd = mk((b, KVH, R, D), dtype, R ** -0.5, gen=gen)
+    v, vd = mk((b, KVH, L, D), dtype, gen=gen)
+    Av, Avd = mk((b, L, 20), dtype, gen=gen)
+    Bv, Bvd = mk((b, KVH, 20, D), dtype, 20 ** -0.5, gen=gen)
+    want = O.qab_rope(q, A, B, theta)
+    for fn in (FR.qAB_rope_v1, FR.qAB_rope_v3, FR.qAB_rope_v4):
+        check(fn(qd, Ad, Bd, theta=theta), want, dtype, fn.__name__)
+    cos, sin = O.rope_cos_sin(D, L, theta)
+    table = torch.cat([sin[:, : D // 2], cos[:, : D // 2]], dim=-1).to(DEV)
+    check(FR.qAB_rope_v2(qd, Ad, Bd, table), want, dtype, "qAB_rope_v2")
+    # fused decode: dense V and factorized V, default 1/sqrt(D) scale
+    check(K.recon_rope_decode(qd, Ad, Bd, vd, theta=theta), O.recon_rope_decode(q, A, B, v, theta), dtype, "recon_rope_decode dense V")
+    check(K.recon_rope_decode(qd, Ad, Bd, Avd, Bvd, theta=theta),
+          O.recon_rope_decode(q, A, B, Av, theta, value_B=Bv), dtype, "recon_rope_decode factorized V")
+    # the reference's own RoPE entry point: unscaled logits (scaled-down q keeps softmax sane)
+    qs, qsd = (q * D ** -0.5).to(dtype), (qd * D ** -0.5).to(dtype)
+    check(K.group_query_attention_factorized_RoPE(qsd, Ad, Bd, Avd, Bvd, theta=theta),
+          O.gqa_factorized_rope(qs, A, B, Av, Bv, theta), dtype, "factorized_RoPE")
+
+
+def test_rope_query_matches_oracle():
+    q, qd = mk((2, 8, 1, 128), torch.bfloat16, gen=g(4))
+    got = K.rope_query(qd, 500000.0, 16384)
+    assert torch.equal(got.cpu(), O.rope_query(q, 500000.0, 16384))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_shared_B_matrix_and_strided_views(dtype):
+    """BASELINE-style shared B (R, KVH*D) broadcast over the batch, and non-contiguous K/V views."""
+    b, H, KVH, D, L, R, theta = 3, 8, 2, 64, 75, 32, 500000.0
+    gen = g(5)
+    q, qd = mk((b, H, 1, D), dtype, gen=gen)
+    A, Ad = mk((b, L, R), dtype, gen=gen)
+    B2, B2d = mk((R, KVH * D), dtype, R ** -0.5, gen=gen)
+    v, vd = mk((b, L, KVH, D), dtype, gen=gen)         # stored token-major, passed as a transposed view
+    B4 = B2.view(R, KVH, D).permute(1, 0, 2)[None].expand(b, -1, -1, -1)
+    want = O.recon_rope_decode(q, A, B4, v.transpose(1, 2), theta)
+    check(K.recon_rope_decode(qd, Ad, B2d, vd.transpose(1, 2), theta=theta), want, dtype, "shared B, strided V")
+    # A as a slice of a wider buffer (row stride != R)
+    wide = torch.zeros(b, L, R + 8, dtype=dtype, device=DEV)
+    wide[..., :R] = Ad
+    check(K.recon_rope_decode(qd, wide[..., :R], B2d, vd.transpose(1, 2), theta=theta), want, dtype, "strided A")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mla_family(dtype):
+    b, H, lora, rope, L = 2, 16, 64, 16, 203
+    gen = g(6)
+    qn, qnd = mk((b, H, lora), dtype, 1 / 3, gen=gen)
+    qr, qrd = mk((b, H, rope), dtype, 1 / 3, gen=gen)
+    c, cd = mk((b, L, 1, lora), dtype, 1 / 3, gen=gen)
+    kr, krd = mk((b, L, 1, rope), dtype, 1 / 3, gen=gen)
+    check(FD.mla2.mla_decode_attention_fwd(qnd, qrd, cd, krd, 0.7), O.mla_decode(qn, qr, c, kr, 0.7), dtype, "mla2 fwd")
+    check(FD.mla2.mla_decode_attention_fwd_ref(qnd, qrd, cd, krd, 2.0), O.mla_decode(qn, qr, c, kr, 0.5), dtype, "mla2 ref (divide)")
+    # factorized latent
+    r = 24
+    kA, kAd = mk((b, L, 1, r), dtype, 1 / 3, gen=gen)
+    kB, kBd = mk((b, 1, r, lora), dtype, 1 / 3, gen=gen)
+    check(FD.mla2.mla_decode_attention_xKV(qnd, qrd, kAd, kBd, krd, 0.7),
+          O.mla_decode_xkv(qn, qr, kA, kB, kr, 0.7), dtype, "mla2 xKV")
+    # packed 576-style cache (here 64+16 = 80), value = the latent prefix, optional logit cap
+    kbuf = torch.cat([c, kr], dim=-1)
+    kbufd = kbuf.to(DEV)
+    qfull, qfulld = torch.cat([qn, qr], dim=-1), torch.cat([qnd, qrd], dim=-1)
+    for cap in (0.0, 5.0):
+        o = torch.zeros(b, H, lora, dtype=dtype, device=DEV)
+        assert FD.mla.decode_attention_fwd(qfulld, kbufd, kbufd[..., :lora], o, 0.9, cap) is None
+        check(o, O.flash_decode_gqa(qfull, kbuf, kbuf[..., :lora], 0.9, logit_cap=cap), dtype, f"mla.decode cap={cap}")
+    check(FD.mla.decode_attention_reference(qfulld, kbufd, kbufd[..., :lora], None, 2.0),
+          O.flash_decode_gqa(qfull, kbuf, kbuf[..., :lora], 0.5), dtype, "mla.decode_attention_reference")
+    # absorbed form with W_uk / W_uv
+    nope, vdim = 32, 48
+    qq, qqd = mk((b, H, nope), dtype, gen=gen)
+    Wk, Wkd = mk((H, nope, lora), dtype, lora ** -0.5, gen=gen)
+    Wv, Wvd = mk((H, lora, vdim), dtype, lora ** -0.5, gen=gen)
+    sc = (nope + rope) ** -0.5
+    check(K.mla_absorbed_decode(qqd, qrd, cd[:, :, 0], krd[:, :, 0], Wkd, Wvd, sc),
+          O.mla_absorbed(qq, qr, c[:, :, 0], kr[:, :, 0], Wk, Wv, sc), dtype, "mla_absorbed_decode")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("factorized_v", [False, True])
+def test_group_decode(dtype, factorized_v):
+    NL, b, H, KVH, D, L, R, Rv, theta = 3, 2, 8, 2, 64, 90, 32, 24, 500000.0
+    gen = g(7)
+    A, Ad = mk((b, L, R), dtype, gen=gen)
+    qs, Bs, Vs, Bvs = [], [], [], []
+    Av, Avd = mk((b, L, Rv), dtype, gen=gen)
+    for _ in range(NL):
+        qs.append(mk((b, H, 1, D), dtype, gen=gen))
+        Bs.append(mk((R, KVH * D), dtype, R ** -0.5, gen=gen))
+        Vs.append(mk((b, KVH, L, D), dtype, gen=gen))
+        Bvs.append(mk((Rv, KVH * D), dtype, Rv ** -0.5, gen=gen))
+    expand = lambda B2, r: B2.view(r, KVH, D).permute(1, 0, 2)[None].expand(b, -1, -1, -1)
+    if factorized_v:
+        got = K.xkv_group_decode([x[1] for x in qs], Ad, [x[1] for x in Bs], Avd, [x[1] for x in Bvs], theta=theta)
+        want = O.group_decode([x[0] for x in qs], A, [expand(x[0], R) for x in Bs], Av,
+                              [expand(x[0], Rv) for x in Bvs], theta)
+    else:
+        got = K.xkv_group_decode([x[1] for x in qs], Ad, [x[1] for x in Bs], [x[1] for x in Vs], theta=theta)
+        want = O.group_decode([x[0] for x in qs], A, [expand(x[0], R) for x in Bs], [x[0] for x in Vs], None, theta)
+    for i in range(NL):
+        check(got[i], want[i], dtype, f"group layer {i}")
+
+
+def test_golden_fixtures_through_cuda():
+    """The committed outputs of the reference's own eager code, reproduced by the CUDA path."""
+    G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_eager.npz"))
+    t = lambda k: torch.from_numpy(G[k])
+    d = lambda k: torch.from_numpy(G[k]).to(DEV)
+    f32 = torch.float32
+    for name in ("a", "b", "c"):
+        p = f"gqa/{name}/"
+        check(K.group_query_attention(d(p + "q"), d(p + "K"), d(p + "V")), t(p + "dense"), f32, p + "dense")
+        check(K.group_query_attention_factorized_v_only(d(p + "q"), d(p + "K"), d(p + "Av"), d(p + "Bv")), t(p + "v_only"), f32, p + "v_only")
+        check(K.group_query_attention_factorized(d(p + "q"), d(p + "Ak"), d(p + "Bk"), d(p + "Av"), d(p + "Bv")), t(p + "factorized"), f32, p + "factorized")
+        check(FR.qAB_no_pe_ref(d(p + "q"), d(p + "Ak"), d(p + "Bk")), t(p + "qab_no_pe"), f32, p + "qab_no_pe")
+        check(FR.gqa_xKV_no_pe_ref(d(p + "q")[:, :, 0], d(p + "Ak"), d(p + "Bk"), d(p + "Av"), d(p + "Bv")), t(p + "fused"), f32, p + "fused")
+        check(FR.gqa_xKV_no_pe_k_only_ref(d(p + "q")[:, :, 0], d(p + "Ak"), d(p + "Bk"), d(p + "V").transpose(1, 2)), t(p + "fused_k_only"), f32, p + "k_only")
+    for name in ("r1", "r2"):
+        p = f"qab_rope/{name}/"
+        theta = float(G[p + "theta"])
+        check(FR.qAB_rope_v1(d(p + "q"), d(p + "Ak"), d(p + "Bk"), theta=theta), t(p + "logits"), f32, p + "logits")
+        check(K.recon_rope_decode(d(p + "q"), d(p + "Ak"), d(p + "Bk"), d(p + "V"), theta=theta), t(p + "decode"), f32, p + "decode")
+    for name in ("m1", "m2"):
+        p = f"mla/{name}/"
+        check(FD.mla2.mla_decode_attention_fwd(d(p + "q_nope"), d(p + "q_rope"), d(p + "kv_nope"), d(p + "k_rope"), 1.0), t(p + "out_scale1"), f32, p)
+        check(FD.mla2.mla_decode_attention_fwd(d(p + "q_nope"), d(p + "q_rope"), d(p + "kv_nope"), d(p + "k_rope"), 0.25), t(p + "out_mul_quarter"), f32, p)
+
+
+def test_split_count_independence_and_determinism():
+    """Size-independent properties: the result does not depend on the KV split count beyond
+    rounding, and repeated calls are bit-identical (fixed merge order)."""
+    dtype = torch.float32
+    b, H, KVH, D, L = 2, 8, 2, 64, 4000
+    gen = g(8)
+    q, qd = mk((b, H, D), dtype, gen=gen)
+    k, kd = mk((b, L, KVH, D), dtype, gen=gen)
+    v, vd = mk((b, L, KVH, D), dtype, gen=gen)
+    outs = []
+    for s in (1, 3, 64, 250):
+        kw = dict(entry="xkv_dense_decode", score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE,
+                  q=qd, k=kd, v=vd, sm_scale=D ** -0.5, num_splits=s)
+        o1 = ops.decode(**kw)
+        o2 = ops.decode(**kw)
+        assert torch.equal(o1, o2)
+        outs.append(o1)
+    for o in outs[1:]:
+        assert (o - outs[0]).abs().max().item() < 2e-6
+    check(outs[0], O.flash_decode_gqa(q, k, v, D ** -0.5), dtype, "split invariance")
+
+
+def test_softmax_shift_invariance_and_extreme_logits():
+    """Large logits must not overflow (online softmax); adding a constant key direction that
+    shifts every logit equally leaves the output unchanged."""
+    dtype = torch.float32
+    b, H, KVH, D, L = 1, 4, 1, 32, 300
+    gen = g(9)
+    q, qd = mk((b, H, 1, D), dtype, 30.0, gen=gen)      # logits of magnitude ~ 1e2-1e3
+    k, kd = mk((b, KVH, L, D), dtype, gen=gen)
+    v, vd = mk((b, KVH, L, D), dtype, gen=gen)
+    got = K.group_query_attention(qd, kd, vd)
+    check(got, O.gqa_dense(q, k, v), dtype, "extreme logits")
+
+
+def test_error_behaviour_on_gpu():
+    q = torch.randn(1, 4, 1, 16, device=DEV)
+    kv = torch.randn(1, 2, 8, 16, device=DEV)
+    with pytest.raises(NotImplementedError):
+        K.group_query_attention(q, kv, kv, attn_mask=torch.zeros(1, 1, 1, 8, device=DEV))
+    with pytest.raises(ValueError):
+        K.group_query_attention(q, kv.half(), kv.half())
+    with pytest.raises(AssertionError):
+        K.group_query_attention(torch.randn(1, 4, 2, 16, device=DEV), kv, kv)
+    with pytest.raises(ValueError):
+        K.group_query_attention(q.double(), kv.double(), kv.double())
+    with pytest.raises(AssertionError):
+        FR.qAB_rope_v1(q, torch.randn(1, 8, 5, device=DEV), torch.randn(1, 2, 6, 16, device=DEV))
