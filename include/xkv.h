@@ -126,6 +126,15 @@ XKV_API size_t xkv_decode_workspace_bytes(const xkv_decode_params* p);
 XKV_API int xkv_decode(const xkv_decode_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Synchronises `stream` and reads back the status words the last xkv_decode() on this workspace
+ * left in its first 32 bytes: returns XKV_OK, or XKV_ERR_TIMEOUT when a bounded device-side
+ * wait expired (detail[1..4], if detail != NULL, then hold role, tile, chunk and step of the
+ * first wait that gave up), or XKV_ERR_LAUNCH when CUDA reports an error.  detail has 8 entries.
+ * No counterpart in the reference (its kernels have no device-side waits).
+ */
+XKV_API int xkv_workspace_status(const void* workspace, void* stream, int32_t* detail);
+
+/*
  * Named entry points.  Each checks that the parameter block describes its operation and
  * then runs xkv_decode(); they exist so that a binding reads like the reference call.
  *

@@ -22,6 +22,7 @@ _DTYPES = {torch.float32: XKV_F32, torch.bfloat16: XKV_BF16, torch.float16: XKV_
 
 EXPORTS = [
     "xkv_version", "xkv_decode_params_size", "xkv_strerror", "xkv_decode_plan", "xkv_decode_workspace_bytes", "xkv_decode",
+    "xkv_workspace_status",
     "xkv_dense_decode", "xkv_absorbed_decode", "xkv_recon_rope_decode", "xkv_qab_logits",
     "xkv_mla_decode", "xkv_group_decode_workspace_bytes", "xkv_group_decode", "xkv_merge",
     "xkv_rope_table",
@@ -99,6 +100,8 @@ def load():
         lib.xkv_rope_table.restype = C.c_int
         lib.xkv_rope_table.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
         lib.xkv_decode_params_size.restype = C.c_size_t
+        lib.xkv_workspace_status.restype = C.c_int
+        lib.xkv_workspace_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
         if lib.xkv_version() != 1:
             raise RuntimeError("libxkv.so version mismatch")
         if lib.xkv_decode_params_size() != C.sizeof(DecodeParams):
@@ -172,6 +175,19 @@ def run_decode(params: DecodeParams, device: torch.device, entry: str = "xkv_dec
     stream = torch.cuda.current_stream(device).cuda_stream
     rc = getattr(lib, entry)(C.byref(params), ws.data_ptr(), ws.numel(), stream)
     check(rc, entry)
+
+
+def last_status(device: torch.device):
+    """Synchronise the current stream and return (status, detail[8]) of the last call that used
+    this (device, stream) workspace."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None:
+        return 0, [0] * 8
+    detail = (C.c_int32 * 8)()
+    rc = load().xkv_workspace_status(buf.data_ptr(), key[1], detail)
+    return rc, list(detail)
 
 
 def plan_name(params: DecodeParams):

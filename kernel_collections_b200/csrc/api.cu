@@ -199,6 +199,15 @@ int xkv_group_decode(const xkv_decode_params* layers, int n, void* ws, size_t ws
   return XKV_OK;
 }
 
+int xkv_workspace_status(const void* workspace, void* stream, int32_t* detail) {
+  if (!workspace) return XKV_ERR_BAD_ARG;
+  int32_t host[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return XKV_ERR_LAUNCH;
+  if (cudaMemcpy(host, workspace, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return XKV_ERR_LAUNCH;
+  if (detail) memcpy(detail, host, sizeof(host));
+  return host[0] > 0 ? XKV_ERR_LAUNCH : host[0];
+}
+
 int xkv_merge(const float* partial_o, const float* lse, void* out, int dtype, int batch, int num_heads,
               int num_splits, int dim, int64_t o_sb, int64_t o_sh, void* stream) {
   if (!partial_o || !lse || !out || batch <= 0 || num_heads <= 0 || num_splits <= 0 || dim <= 0)

@@ -52,9 +52,10 @@ __device__ __forceinline__ float warp_max(float v) {
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void absorb_query_kernel(const xkv_decode_params p, float* __restrict__ qeff,
-                                    int score_dim) {
+                                    int score_dim, int* __restrict__ status) {
   extern __shared__ float q_s[];
   const int h = blockIdx.x, b = blockIdx.y;
+  if (h == 0 && b == 0 && threadIdx.x < 8) status[threadIdx.x] = 0;  // this path never waits: always "ok"
   const T* q = static_cast<const T*>(p.q) + (int64_t)b * p.q_sb + (int64_t)h * p.q_sh;
   float* out = qeff + ((int64_t)b * p.num_heads + h) * score_dim;
   for (int d = threadIdx.x; d < p.head_dim; d += blockDim.x) q_s[d] = ldf(q + d);
@@ -366,7 +367,8 @@ int run_generic(const xkv_decode_params& p, const GenericPlan& pl, void* ws, cud
   float* qeff = reinterpret_cast<float*>(w + pl.off_qeff);
   float* partial = reinterpret_cast<float*>(w + pl.off_partial);
   float* lse = reinterpret_cast<float*>(w + pl.off_lse);
-  absorb_query_kernel<T><<<dim3(p.num_heads, p.batch), 128, p.head_dim * sizeof(float), st>>>(p, qeff, pl.score_dim);
+  absorb_query_kernel<T><<<dim3(p.num_heads, p.batch), 128, p.head_dim * sizeof(float), st>>>(
+      p, qeff, pl.score_dim, reinterpret_cast<int*>(w));
   PartialGeom g{pl.heads_per_cta, pl.num_splits, pl.split_len, pl.score_dim, pl.acc_dim};
   // opt in to the large dynamic shared-memory carve-out (per device, cheap, idempotent)
   if (cudaFuncSetAttribute(decode_partial_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -430,7 +432,7 @@ bool generic_plan(const xkv_decode_params& p, GenericPlan* pl) {
   if (S < 1) S = 1;
   pl->split_len = ceil_div(tiles, S) * TT;
   pl->num_splits = ceil_div(p.kv_len, pl->split_len);
-  size_t off = 0;
+  size_t off = 256;  // status words lead every workspace
   pl->off_qeff = off;
   off += align_up((size_t)p.batch * p.num_heads * pl->score_dim * sizeof(float), 256);
   pl->off_partial = off;

@@ -1,6 +1,767 @@
+// Fused key reconstruction + RoPE + decode attention on the sm_100a tensor cores.
+//
+// Per 128-token tile of one batch row the keys of all KV heads are rebuilt as K = A_tile . B on
+// tcgen05 (A: the latent tile, K-major; B: MN-major slices of the projection; fp32 accumulators in
+// TMEM, two 128x256 buffers), rotated in registers straight out of TMEM, dotted with the query
+// heads, pushed through an online softmax and multiplied into a dense V tile.  K never exists
+// in shared or global memory.  One CTA per (KV split, batch row), twelve warps with fixed roles:
+//
+//   warp 0      TMA producer for the A / B operand ring (3 stages of 64 ranks)
+//   warp 1      tcgen05.mma issuer (one elected thread), commits to mbarriers
+//   warp 2      TMEM allocation, TMA producer for the V ring (2 slots of 128 tokens x 1 KV head)
+//   warp 3      idle
+//   warps 4-7   epilogue: tcgen05.ld, RoPE from the {cos,sin} table, q-dot, online softmax, P->smem
+//   warps 8-11  P.V with mma.sync out of shared memory, running output / row-sum accumulators
+//
+// Every mbarrier wait is bounded: on expiry the kernel raises a shared abort flag, records where
+// it gave up in the status words of the workspace, lets every role drain to the common exit,
+// waits for copies in flight, frees its TMEM and returns.  No TMA load uses cluster multicast.
 #include "xkv_internal.h"
+#include <cuda.h>
+#include <math_constants.h>
+
 namespace xkv {
-bool recon_tc_supported(const xkv_decode_params&) { return false; }
-bool recon_tc_plan(const xkv_decode_params&, ReconTcPlan*) { return false; }
-int recon_tc_decode(const xkv_decode_params&, const ReconTcPlan&, void*, cudaStream_t) { return XKV_ERR_UNSUPPORTED; }
+namespace {
+
+constexpr int TILE_M = 128;   // tokens per tile == TMEM lanes
+constexpr int BK = 64;        // ranks per pipeline stage (one 128-byte swizzle row)
+constexpr int D = 128;        // head dim
+constexpr int KVH = 8;        // KV heads
+constexpr int NCH = KVH / 2;  // chunks of two KV heads (256 accumulator columns)
+constexpr int STAGES = 3;
+constexpr int A_BYTES = TILE_M * BK * 2;       // 16 KB
+constexpr int B_BOX = BK * 64 * 2;             // 8 KB: 64 n x 64 k
+constexpr int B_BYTES = 4 * B_BOX;             // 32 KB: 256 n x 64 k
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES; // 48 KB
+constexpr int V_SLOT = TILE_M * D * 2;         // 32 KB
+constexpr int V_SLOTS = 2;
+constexpr int P_PITCH = TILE_M * 2 + 16;       // bytes per head row of P (padded against bank conflicts)
+constexpr int NTHREADS = 384;
+constexpr uint32_t MAX_POLLS = 1u << 26;
+constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;
+
+constexpr int OFF_STAGE = 0;
+constexpr int OFF_V = OFF_STAGE + STAGES * STAGE_BYTES;          // 147456
+constexpr int OFF_Q = OFF_V + V_SLOTS * V_SLOT;                  // 212992
+constexpr int Q_BYTES = 2 * 64 * 8 * 2 * 4;                      // 8192 (G <= 8)
+constexpr int OFF_P = OFF_Q + Q_BYTES;                           // 221184
+constexpr int P_BUF = 16 * P_PITCH;                              // 4352
+constexpr int OFF_WMAX = OFF_P + 2 * P_BUF;                      // 229888
+constexpr int OFF_ALPHA = OFF_WMAX + 2 * 4 * 16 * 4;             // +512
+constexpr int OFF_M = OFF_ALPHA + 2 * 16 * 4;                    // +128
+constexpr int OFF_BAR = OFF_M + 64 * 4;                          // +256
+constexpr int NUM_BARS = 2 * STAGES + 4 + 4 + 4;
+constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
+constexpr int SMEM_USED = OFF_MISC + 16;
+constexpr int SMEM_BYTES = SMEM_USED + 1024;                     // + slack to align the base to 1024
+static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
+
+// status words in the workspace
+enum { ST_CODE = 0, ST_ROLE = 1, ST_TILE = 2, ST_CHUNK = 3, ST_EXTRA = 4 };
+
+struct Args {
+  int batch, kv_len, num_heads, rank;
+  int num_splits, tiles_per_row;
+  float q_scale;
+  const void* q;
+  int64_t q_sb, q_sh;
+  const float2* table;   // [kv_len][64] {cos, sin}
+  float* partial_o;      // [batch][H][splits][128]
+  float* lse;            // [batch][H][splits]
+  void* logits;
+  int64_t lg_sb, lg_sh;
+  int* status;
+  int b_batched;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait (about one second of wall time).  Returns false when the limit is hit (and raises
+// the abort flag) or when another role has already raised it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t it = 0; it < MAX_POLLS; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if ((it & 31u) == 31u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+      __nanosleep(32);
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+// Barrier over the 128 epilogue threads that also agrees on the abort flag, so that either all of
+// them leave or none does (a thread that left alone would strand the rest at the next barrier).
+__device__ __forceinline__ bool epilogue_sync_aborted(volatile int* abort_flag) {
+  const uint32_t mine = *abort_flag ? 1u : 0u;
+  uint32_t any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(any)
+      : "r"(mine)
+      : "memory");
+  return any != 0;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (SWIZZLE_128B, descriptor version 1).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
+  d |= (uint64_t)(sbo_bytes >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+template <typename T> struct TypeTraits;
+template <> struct TypeTraits<__nv_bfloat16> {
+  static constexpr uint32_t kFmt = 1;
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ uint32_t ones2() { return 0x3F803F80u; }
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+template <> struct TypeTraits<__half> {
+  static constexpr uint32_t kFmt = 0;
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ uint32_t ones2() { return 0x3C003C00u; }
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+
+__device__ __forceinline__ void report(int* status, int code, int role, int tile, int chunk, int extra) {
+  if (atomicCAS(&status[ST_CODE], 0, code) == 0) {
+    status[ST_ROLE] = role;
+    status[ST_TILE] = tile;
+    status[ST_CHUNK] = chunk;
+    status[ST_EXTRA] = extra;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+template <typename T, int G, bool LOGITS_ONLY>
+__global__ void __launch_bounds__(NTHREADS, 1)
+recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmV, const Args a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x, b = blockIdx.y;
+  const int tile_begin = (int)(((int64_t)split * a.tiles_per_row) / a.num_splits);
+  const int tile_end = (int)(((int64_t)(split + 1) * a.tiles_per_row) / a.num_splits);
+  const int KB = a.rank / BK;
+
+  const uint32_t bar0 = base + OFF_BAR;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto bar_tfull = [&](int i) { return bar0 + 8u * (2 * STAGES + i); };
+  auto bar_tempty = [&](int i) { return bar0 + 8u * (2 * STAGES + 2 + i); };
+  auto bar_vfull = [&](int i) { return bar0 + 8u * (2 * STAGES + 4 + i); };
+  auto bar_vempty = [&](int i) { return bar0 + 8u * (2 * STAGES + 6 + i); };
+  auto bar_pfull = [&](int i) { return bar0 + 8u * (2 * STAGES + 8 + i); };
+  auto bar_pempty = [&](int i) { return bar0 + 8u * (2 * STAGES + 10 + i); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + OFF_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 4);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_tfull(i), 1);
+      mbar_init(bar_tempty(i), 128);
+      mbar_init(bar_vfull(i), 1);
+      mbar_init(bar_vempty(i), 128);
+      mbar_init(bar_pfull(i), 128);
+      mbar_init(bar_pempty(i), 128);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + OFF_MISC), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (threadIdx.x >= 128 && threadIdx.x < 256) {   // running maxima start at -inf
+    float* m_s = reinterpret_cast<float*>(sm + OFF_M);
+    if (threadIdx.x - 128 < 64) m_s[threadIdx.x - 128] = -CUDART_INF_F;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // =========================== operand producer =============================================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const int bb = a.b_batched ? b : 0;
+      for (int tile = tile_begin; tile < tile_end; ++tile) {
+        for (int c = 0; c < NCH; ++c) {
+          for (int kb = 0; kb < KB; ++kb) {
+            if (!mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag)) {
+              report(a.status, XKV_ERR_TIMEOUT, 0, tile, c, kb);
+              goto producer_done;
+            }
+            mbar_expect_tx(bar_full(stage), STAGE_BYTES);
+            const uint32_t sa = base + OFF_STAGE + stage * STAGE_BYTES;
+            tma_load_3d(sa, &tmA, kb * BK, tile * TILE_M, b, bar_full(stage));
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              tma_load_4d(sa + A_BYTES + i * B_BOX, &tmB, (i & 1) * 64, kb * BK, 2 * c + (i >> 1), bb, bar_full(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
+  producer_done:;
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===================================================
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, A K-major, B MN-major, N = 256, M = 128
+      const uint32_t idesc = (1u << 4) | (TypeTraits<T>::kFmt << 7) | (TypeTraits<T>::kFmt << 10) | (1u << 16) |
+                             ((256u >> 3) << 17) | ((128u >> 4) << 24);
+      int stage = 0, abuf = 0;
+      uint32_t phase = 0, aphase = 0;
+      for (int tile = tile_begin; tile < tile_end; ++tile) {
+        for (int c = 0; c < NCH; ++c) {
+          if (!mbar_wait(bar_tempty(abuf), aphase ^ 1u, abort_flag)) {
+            report(a.status, XKV_ERR_TIMEOUT, 1, tile, c, -1);
+            goto mma_done;
+          }
+          tc_fence_after();
+          const uint32_t tacc = tmem_base + (uint32_t)abuf * 256u;
+          for (int kb = 0; kb < KB; ++kb) {
+            if (!mbar_wait(bar_full(stage), phase, abort_flag)) {
+              report(a.status, XKV_ERR_TIMEOUT, 1, tile, c, kb);
+              goto mma_done;
+            }
+            tc_fence_after();
+            const uint32_t sa = base + OFF_STAGE + stage * STAGE_BYTES;
+#pragma unroll
+            for (int k4 = 0; k4 < BK / 16; ++k4) {
+              const uint64_t da = smem_desc(sa + k4 * 32, 16, 1024);
+              const uint64_t db = smem_desc(sa + A_BYTES + k4 * 2048, B_BOX, 1024);
+              tc_mma(tacc, da, db, idesc, (kb | k4) != 0 ? 1u : 0u);
+            }
+            tc_commit(bar_empty(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          tc_commit(bar_tfull(abuf));
+          abuf ^= 1;
+          if (abuf == 0) aphase ^= 1u;
+        }
+      }
+    }
+  mma_done:;
+  } else if (warp == 2) {
+    // =========================== V producer ===================================================
+    if (!LOGITS_ONLY && lane == 0) {
+      int slot = 0;
+      uint32_t ph = 0;
+      for (int tile = tile_begin; tile < tile_end; ++tile) {
+        for (int kvh = 0; kvh < KVH; ++kvh) {
+          if (!mbar_wait(bar_vempty(slot), ph ^ 1u, abort_flag)) {
+            report(a.status, XKV_ERR_TIMEOUT, 2, tile, kvh, -1);
+            goto vprod_done;
+          }
+          mbar_expect_tx(bar_vfull(slot), V_SLOT);
+          const uint32_t sv = base + OFF_V + slot * V_SLOT;
+          tma_load_4d(sv, &tmV, 0, kvh, tile * TILE_M, b, bar_vfull(slot));
+          tma_load_4d(sv + V_SLOT / 2, &tmV, 64, kvh, tile * TILE_M, b, bar_vfull(slot));
+          if (++slot == V_SLOTS) { slot = 0; ph ^= 1u; }
+        }
+      }
+    }
+  vprod_done:;
+  } else if (warp >= 4 && warp < 8) {
+    // =========================== epilogue =====================================================
+    const int et = threadIdx.x - 128;
+    const int ew = et >> 5;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(ew * 32) << 16);
+    float* q_s = reinterpret_cast<float*>(sm + OFF_Q);
+    float* wmax_s = reinterpret_cast<float*>(sm + OFF_WMAX);
+    float* alpha_s = reinterpret_cast<float*>(sm + OFF_ALPHA);
+    float* m_s = reinterpret_cast<float*>(sm + OFF_M);
+    const T* qg = static_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
+    int abuf = 0, pbuf = 0, par = 0;
+    uint32_t aphase = 0, pphase = 0;
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+      const int tok = tile * TILE_M + et;
+      const bool valid = tok < a.kv_len;
+      const float4* tab = reinterpret_cast<const float4*>(a.table + (int64_t)min(tok, a.kv_len - 1) * 64);
+      for (int c = 0; c < NCH; ++c) {
+        // ---- stage this chunk's queries: q_s[hh][j][g][{j, j+64}] = q * scale -----------------
+        if (epilogue_sync_aborted(abort_flag)) goto epi_done;
+        for (int idx = et; idx < 2 * G * D; idx += 128) {
+          const int hh = idx / (G * D), g = (idx / D) % G, d = idx % D;
+          const float v = TypeTraits<T>::to_f(qg[(int64_t)((2 * c + hh) * G + g) * a.q_sh + d]) * a.q_scale;
+          q_s[((hh * 64 + (d & 63)) * G + g) * 2 + (d >> 6)] = v;
+        }
+        float m_old[2 * G];
+        if (!LOGITS_ONLY) {
+#pragma unroll
+          for (int i = 0; i < 2 * G; ++i) m_old[i] = m_s[c * 2 * G + i];
+        }
+        if (epilogue_sync_aborted(abort_flag)) goto epi_done;
+        if (!mbar_wait(bar_tfull(abuf), aphase, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 4, tile, c, 0);
+        tc_fence_after();
+
+        float s[2 * G];
+#pragma unroll
+        for (int i = 0; i < 2 * G; ++i) s[i] = 0.f;
+#pragma unroll 1
+        for (int jb = 0; jb < 4; ++jb) {
+          float4 cs[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) cs[i] = __ldg(tab + jb * 8 + i);
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t x0[16], x1[16];
+            const uint32_t col = (uint32_t)abuf * 256u + hh * 128 + jb * 16;
+            tmem_ld16(lane_addr + col, x0);
+            tmem_ld16(lane_addr + col + 64, x1);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float cc = (i & 1) ? cs[i >> 1].z : cs[i >> 1].x;
+              const float sn = (i & 1) ? cs[i >> 1].w : cs[i >> 1].y;
+              const float k0 = __uint_as_float(x0[i]), k1 = __uint_as_float(x1[i]);
+              const float r0 = k0 * cc - k1 * sn;
+              const float r1 = k1 * cc + k0 * sn;
+              const float2* qp = reinterpret_cast<const float2*>(q_s + ((hh * 64 + jb * 16 + i) * G) * 2);
+#pragma unroll
+              for (int g = 0; g < G; ++g) {
+                const float2 qq = qp[g];
+                s[hh * G + g] = fmaf(qq.x, r0, fmaf(qq.y, r1, s[hh * G + g]));
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(bar_tempty(abuf));
+        abuf ^= 1;
+        if (abuf == 0) aphase ^= 1u;
+
+        if (LOGITS_ONLY) {
+          if (valid) {
+            T* lg = static_cast<T*>(a.logits) + (int64_t)b * a.lg_sb + tok;
+#pragma unroll
+            for (int i = 0; i < 2 * G; ++i) lg[(int64_t)(2 * c * G + i) * a.lg_sh] = TypeTraits<T>::from_f(s[i]);
+          }
+        } else {
+          // ---- online softmax over the tile, per head -------------------------------------------
+#pragma unroll
+          for (int i = 0; i < 2 * G; ++i) {
+            if (!valid) s[i] = -CUDART_INF_F;
+            float wm = s[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+            if (lane == 0) wmax_s[(par * 4 + ew) * 16 + i] = wm;
+          }
+          if (epilogue_sync_aborted(abort_flag)) goto epi_done;
+          float m_new[2 * G];
+#pragma unroll
+          for (int i = 0; i < 2 * G; ++i) {
+            float mx = m_old[i];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mx = fmaxf(mx, wmax_s[(par * 4 + w) * 16 + i]);
+            m_new[i] = mx;
+          }
+          par ^= 1;
+          if (!mbar_wait(bar_pempty(pbuf), pphase ^ 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 4, tile, c, 1);
+          T* p_s = reinterpret_cast<T*>(sm + OFF_P + pbuf * P_BUF);
+#pragma unroll
+          for (int i = 0; i < 2 * G; ++i)
+            p_s[i * (P_PITCH / 2) + et] = TypeTraits<T>::from_f(exp2f(s[i] - m_new[i]));
+          if (et == 0) {
+#pragma unroll
+            for (int i = 0; i < 2 * G; ++i) {
+              alpha_s[pbuf * 16 + i] = exp2f(m_old[i] - m_new[i]);
+              m_s[c * 2 * G + i] = m_new[i];
+            }
+          }
+          mbar_arrive(bar_pfull(pbuf));
+          pbuf ^= 1;
+          if (pbuf == 0) pphase ^= 1u;
+        }
+      }
+    }
+  epi_done:;
+  } else if (warp >= 8) {
+    // =========================== P.V ==========================================================
+    if (!LOGITS_ONLY) {
+      const int pw = warp - 8;
+      const int g = lane >> 2, t = lane & 3;
+      float acc[KVH][2][4];
+      float lacc[KVH][4];
+#pragma unroll
+      for (int k = 0; k < KVH; ++k) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { acc[k][0][i] = 0.f; acc[k][1][i] = 0.f; lacc[k][i] = 0.f; }
+      }
+      const float* alpha_s = reinterpret_cast<const float*>(sm + OFF_ALPHA);
+      const float* m_s = reinterpret_cast<const float*>(sm + OFF_M);
+      const uint32_t ones[4] = {TypeTraits<T>::ones2(), TypeTraits<T>::ones2(), TypeTraits<T>::ones2(),
+                                TypeTraits<T>::ones2()};
+      int slot = 0, pbuf = 0;
+      uint32_t vph = 0, pph = 0;
+      bool alive = true;
+      for (int tile = tile_begin; tile < tile_end && alive; ++tile) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          bool ok = mbar_wait(bar_pfull(pbuf), pph, abort_flag);
+          if (!__all_sync(0xffffffffu, ok)) {
+            if (lane == 0) report(a.status, XKV_ERR_TIMEOUT, 8, tile, c, 0);
+            alive = false;
+            break;
+          }
+          const uint32_t p_base = base + OFF_P + pbuf * P_BUF;
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int kvh = 2 * c + hh;
+            ok = mbar_wait(bar_vfull(slot), vph, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) {
+              if (lane == 0) report(a.status, XKV_ERR_TIMEOUT, 8, tile, c, 1 + hh);
+              alive = false;
+              break;
+            }
+            const float al0 = (2 * t < G) ? alpha_s[pbuf * 16 + hh * G + 2 * t] : 1.f;
+            const float al1 = (2 * t + 1 < G) ? alpha_s[pbuf * 16 + hh * G + 2 * t + 1] : 1.f;
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+              acc[kvh][mt][0] *= al0; acc[kvh][mt][1] *= al1;
+              acc[kvh][mt][2] *= al0; acc[kvh][mt][3] *= al1;
+            }
+            lacc[kvh][0] *= al0; lacc[kvh][1] *= al1; lacc[kvh][2] *= al0; lacc[kvh][3] *= al1;
+            const uint32_t v_base = base + OFF_V + slot * V_SLOT;
+            // ldmatrix row of this lane: matrix mi = lane / 8, row r = lane % 8
+            const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+            for (int ks = 0; ks < TILE_M / 16; ++ks) {
+              uint32_t b0 = 0, b1 = 0;
+              if (g < G) {
+                const uint32_t pa = p_base + (hh * G + g) * P_PITCH + (ks * 16 + 2 * t) * 2;
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b0) : "r"(pa));
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b1) : "r"(pa + 16));
+              }
+#pragma unroll
+              for (int mt = 0; mt < 2; ++mt) {
+                const int token = ks * 16 + (mi >> 1) * 8 + r;
+                const int dim = pw * 32 + mt * 16 + (mi & 1) * 8;
+                const uint32_t va = v_base + (dim >> 6) * (V_SLOT / 2) + token * 128 +
+                                    ((((dim & 63) >> 3) ^ (token & 7)) << 4);
+                uint32_t af[4];
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(af[0]), "=r"(af[1]), "=r"(af[2]), "=r"(af[3])
+                             : "r"(va));
+                TypeTraits<T>::mma(acc[kvh][mt], af, b0, b1);
+              }
+              TypeTraits<T>::mma(lacc[kvh], ones, b0, b1);
+            }
+            // The slot is refilled by TMA (async proxy) while it was read with ldmatrix (generic
+            // proxy): a cross-proxy fence must separate this warp's reads from the release,
+            // otherwise a refill can land under reads that are still in flight.
+            __syncwarp();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(bar_vempty(slot));
+            if (++slot == V_SLOTS) { slot = 0; vph ^= 1u; }
+          }
+          if (!alive) break;
+          mbar_arrive(bar_pempty(pbuf));
+          pbuf ^= 1;
+          if (pbuf == 0) pph ^= 1u;
+        }
+      }
+      if (alive && tile_end > tile_begin) {
+        // normalised partial output and log-sum-exp of this split
+        const int H = KVH * G;
+#pragma unroll
+        for (int kvh = 0; kvh < KVH; ++kvh) {
+#pragma unroll
+          for (int n = 0; n < 2; ++n) {
+            const int hd = 2 * t + n;
+            if (hd < G) {
+              const int h = kvh * G + hd;
+              const float l = lacc[kvh][n];
+              const float inv = l > 0.f ? 1.f / l : 0.f;
+              float* po = a.partial_o + (((int64_t)b * H + h) * a.num_splits + split) * D;
+#pragma unroll
+              for (int mt = 0; mt < 2; ++mt) {
+                const int dim = pw * 32 + mt * 16 + g;
+                po[dim] = acc[kvh][mt][n] * inv;
+                po[dim + 8] = acc[kvh][mt][2 + n] * inv;
+              }
+              if (pw == 0 && g == 0)
+                a.lse[((int64_t)b * H + h) * a.num_splits + split] =
+                    l > 0.f ? (m_s[h] + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // =========================== common exit =====================================================
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies and MMAs that may still be in flight time to land before the CTA's shared
+    // memory and TMEM are released
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+__global__ void clear_status_kernel(int* status) {
+  if (threadIdx.x < 8) status[threadIdx.x] = 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (tried) return fn;
+  tried = true;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+      q == cudaDriverEntryPointSuccess)
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  else
+    cudaGetLastError();
+  return fn;
+}
+
+bool encode(CUtensorMap* m, int dtype, int rank, const void* ptr, const cuuint64_t* dims, const cuuint64_t* strides,
+            const cuuint32_t* box) {
+  EncodeTiledFn fn = get_encode();
+  if (!fn) return false;
+  cuuint32_t es[5] = {1, 1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == XKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(m, dt, (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool stride_ok(int64_t elems) { return elems > 0 && (elems * 2) % 16 == 0; }
+
+template <typename T, int G, bool LO>
+int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tV, const Args& args, cudaStream_t st) {
+  auto kern = recon_tc_kernel<T, G, LO>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
+    cudaGetLastError();
+    return XKV_ERR_LAUNCH;
+  }
+  kern<<<dim3(args.num_splits, args.batch), NTHREADS, SMEM_BYTES, st>>>(tA, tB, tV, args);
+  return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
+}
+
+}  // namespace
+
+bool recon_tc_supported(const xkv_decode_params& p) {
+  if (p.score_mode != XKV_SCORE_RECON_ROPE) return false;
+  if (p.dtype != XKV_BF16 && p.dtype != XKV_F16) return false;
+  if (p.head_dim != D || p.num_kv_heads != KVH || p.k_proj_heads != KVH) return false;
+  const int G = p.num_heads / p.num_kv_heads;
+  if (G != 4 && G != 8) return false;
+  if (p.k_rank < BK || p.k_rank % BK != 0) return false;
+  if (p.tail_dim != 0 || p.logit_cap > 0.f) return false;
+  if (p.kp_sd != 1 || !aligned16(p.k) || !aligned16(p.k_proj) || !aligned16(p.q)) return false;
+  if (!stride_ok(p.k_sl) || (p.batch > 1 && !stride_ok(p.k_sb))) return false;
+  if (!stride_ok(p.kp_sr) || !stride_ok(p.kp_sh)) return false;
+  if (p.kp_sb != 0 && !stride_ok(p.kp_sb)) return false;
+  if (p.q_sh < D) return false;
+  if (!(p.flags & XKV_FLAG_LOGITS_ONLY)) {
+    if (p.value_mode != XKV_VALUE_DENSE || p.value_dim != D) return false;
+    if (!aligned16(p.v) || !stride_ok(p.v_sl) || !stride_ok(p.v_sh)) return false;
+    if (p.batch > 1 && !stride_ok(p.v_sb)) return false;
+  }
+  return true;
+}
+
+bool recon_tc_plan(const xkv_decode_params& p, ReconTcPlan* pl) {
+  const int tiles = ceil_div(p.kv_len, TILE_M);
+  const int sms = device_sm_count();
+  int best_s = 1;
+  int64_t best_cost = -1;
+  const int max_s = tiles < 64 ? tiles : 64;
+  for (int s = 1; s <= max_s; ++s) {
+    const int64_t waves = ceil_div(p.batch * s, sms);
+    const int64_t cost = waves * ceil_div(tiles, s);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = s; }
+  }
+  pl->num_splits = best_s;
+  pl->tiles_per_split = tiles;   // tiles per batch row; the kernel cuts [s*T/S, (s+1)*T/S)
+  size_t off = 256;              // status words
+  pl->off_table = off;
+  if (!p.rope_table) off += align_up((size_t)p.kv_len * (D / 2) * sizeof(float2), 256);
+  pl->off_partial = off;
+  const bool lo = (p.flags & XKV_FLAG_LOGITS_ONLY) != 0;
+  if (!lo) off += align_up((size_t)p.batch * p.num_heads * best_s * D * sizeof(float), 256);
+  pl->off_lse = off;
+  if (!lo) off += align_up((size_t)p.batch * p.num_heads * best_s * sizeof(float), 256);
+  pl->total_bytes = off;
+  return true;
+}
+
+int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& pl, void* ws, cudaStream_t st) {
+  char* w = static_cast<char*>(ws);
+  if (!aligned16(w)) return XKV_ERR_ALIGN;
+  const bool lo = (p.flags & XKV_FLAG_LOGITS_ONLY) != 0;
+  const int G = p.num_heads / p.num_kv_heads;
+
+  CUtensorMap tA, tB, tV;
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)p.k_rank, (cuuint64_t)p.kv_len, (cuuint64_t)p.batch};
+    const int64_t sb = p.batch > 1 ? p.k_sb : (int64_t)p.kv_len * p.k_sl;
+    const cuuint64_t strides[2] = {(cuuint64_t)p.k_sl * 2, (cuuint64_t)sb * 2};
+    const cuuint32_t box[3] = {BK, TILE_M, 1};
+    if (!encode(&tA, p.dtype, 3, p.k, dims, strides, box)) return XKV_ERR_NO_DEVICE;
+  }
+  const int b_batched = (p.kp_sb != 0 && p.batch > 1) ? 1 : 0;
+  {
+    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)p.k_rank, (cuuint64_t)KVH, (cuuint64_t)(b_batched ? p.batch : 1)};
+    const int64_t sb = b_batched ? p.kp_sb : (int64_t)KVH * p.k_rank * D * 4;
+    const cuuint64_t strides[3] = {(cuuint64_t)p.kp_sr * 2, (cuuint64_t)p.kp_sh * 2, (cuuint64_t)sb * 2};
+    const cuuint32_t box[4] = {64, BK, 1, 1};
+    if (!encode(&tB, p.dtype, 4, p.k_proj, dims, strides, box)) return XKV_ERR_NO_DEVICE;
+  }
+  if (!lo) {
+    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)KVH, (cuuint64_t)p.kv_len, (cuuint64_t)p.batch};
+    const int64_t sb = p.batch > 1 ? p.v_sb : (int64_t)p.kv_len * KVH * D * 4;
+    const cuuint64_t strides[3] = {(cuuint64_t)p.v_sh * 2, (cuuint64_t)p.v_sl * 2, (cuuint64_t)sb * 2};
+    const cuuint32_t box[4] = {64, 1, TILE_M, 1};
+    if (!encode(&tV, p.dtype, 4, p.v, dims, strides, box)) return XKV_ERR_NO_DEVICE;
+  } else {
+    tV = tA;
+  }
+
+  int* status = reinterpret_cast<int*>(w);
+  clear_status_kernel<<<1, 32, 0, st>>>(status);
+  const float2* table = reinterpret_cast<const float2*>(p.rope_table);
+  if (!table) {
+    float* tb = reinterpret_cast<float*>(w + pl.off_table);
+    int rc = launch_rope_table(tb, p.kv_len, D / 2, p.pos_offset, p.theta, p.inv_freq, st);
+    if (rc != XKV_OK) return rc;
+    table = reinterpret_cast<const float2*>(tb);
+  }
+
+  Args a;
+  a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = p.num_heads; a.rank = p.k_rank;
+  a.num_splits = pl.num_splits; a.tiles_per_row = pl.tiles_per_split;
+  a.q_scale = lo ? p.sm_scale : p.sm_scale * 1.4426950408889634f;
+  a.q = p.q; a.q_sb = p.q_sb; a.q_sh = p.q_sh;
+  a.table = table;
+  a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
+  a.lse = reinterpret_cast<float*>(w + pl.off_lse);
+  a.logits = p.logits; a.lg_sb = p.lg_sb; a.lg_sh = p.lg_sh;
+  a.status = status;
+  a.b_batched = b_batched;
+
+  int rc;
+#define XKV_TC(T, GG)                                                        \
+  rc = lo ? launch<T, GG, true>(tA, tB, tV, a, st) : launch<T, GG, false>(tA, tB, tV, a, st)
+  if (p.dtype == XKV_BF16) {
+    if (G == 4) { XKV_TC(__nv_bfloat16, 4); } else { XKV_TC(__nv_bfloat16, 8); }
+  } else {
+    if (G == 4) { XKV_TC(__half, 4); } else { XKV_TC(__half, 8); }
+  }
+#undef XKV_TC
+  if (rc != XKV_OK) return rc;
+  if (lo) return XKV_OK;
+  return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, D, D, nullptr, 1,
+                      0, 0, 0, 0, p.o_sb, p.o_sh, st);
+}
+
+}  // namespace xkv

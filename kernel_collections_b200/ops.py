@@ -23,8 +23,7 @@ def _inner_contig(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
 
 
 def _stride(t: torch.Tensor, dim: int) -> int:
-    # a size-1 (or expanded) dimension may carry any stride; 0 keeps the arithmetic harmless
-    return 0 if t.shape[dim] == 1 else t.stride(dim)
+    return t.stride(dim)
 
 
 def build_params(
@@ -88,6 +87,8 @@ def build_params(
             p.k_proj_heads = k_proj.shape[1]
             p.k_proj = k_proj.data_ptr()
             p.kp_sb, p.kp_sh, p.kp_sr, p.kp_sd = (_stride(k_proj, i) for i in range(4))
+            if k_proj.shape[0] == 1:
+                p.kp_sb = 0          # one matrix shared by the whole batch
             if p.kp_sd == 0:
                 p.kp_sd = 1
             if KVH is None:
@@ -123,6 +124,8 @@ def build_params(
                 p.value_dim = v_proj.shape[3]
                 p.v_proj = v_proj.data_ptr()
                 p.vp_sb, p.vp_sh, p.vp_sr, p.vp_sd = (_stride(v_proj, i) for i in range(4))
+                if v_proj.shape[0] == 1:
+                    p.vp_sb = 0
                 if p.vp_sd == 0:
                     p.vp_sd = 1
                 if KVH is None:
