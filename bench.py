@@ -115,14 +115,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-rows", type=int, default=4, help="batch rows of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--small", action="store_true", help="context 2048 (profiling-sized case)")
+    ap.add_argument("--small", action="store_true", help="context 4096 (profiling-sized case, 0.2 GB of inputs)")
     ap.add_argument("--force-generic", action="store_true")
     args = ap.parse_args()
 
     from kernel_collections_b200 import synthetic
     cfg = synthetic.ReconRopeConfig()
     if args.small:
-        cfg = cfg.scaled(kv_len=2048, name="c2_small_L2048")
+        cfg = cfg.scaled(kv_len=4096, name="c2_small_L4096")
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -10,7 +10,8 @@
 //   warp 1      tcgen05.mma issuer (one elected thread), commits to mbarriers
 //   warp 2      TMEM allocation, TMA producer for the V ring (2 slots of 128 tokens x 1 KV head)
 //   warp 3      idle
-//   warps 4-7   epilogue: tcgen05.ld, RoPE from the {cos,sin} table, q-dot, online softmax, P->smem
+//   warps 4-7   epilogue: tcgen05.ld, RoPE (angles reduced mod 2pi, sin/cos on the SFU), q-dot,
+//               online softmax, P->smem
 //   warps 8-11  P.V with mma.sync out of shared memory, running output / row-sum accumulators
 //
 // Every mbarrier wait is bounded: on expiry the kernel raises a shared abort flag, records where
@@ -52,7 +53,8 @@ constexpr int OFF_M = OFF_ALPHA + 2 * 16 * 4;                    // +128
 constexpr int OFF_BAR = OFF_M + 64 * 4;                          // +256
 constexpr int NUM_BARS = 2 * STAGES + 4 + 4 + 4;
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
-constexpr int SMEM_USED = OFF_MISC + 16;
+constexpr int OFF_FREQ = OFF_MISC + 16;                          // 64 RoPE frequencies
+constexpr int SMEM_USED = OFF_FREQ + 64 * 4;
 constexpr int SMEM_BYTES = SMEM_USED + 1024;                     // + slack to align the base to 1024
 static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
 
@@ -65,7 +67,9 @@ struct Args {
   float q_scale;
   const void* q;
   int64_t q_sb, q_sh;
-  const float2* table;   // [kv_len][64] {cos, sin}
+  const float* inv_freq; // 64 RoPE frequencies (device) or NULL -> theta
+  float theta;
+  int pos_offset;
   float* partial_o;      // [batch][H][splits][128]
   float* lse;            // [batch][H][splits]
   void* logits;
@@ -182,6 +186,18 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
+// sin / cos of an fp32 angle of any magnitude met here (|x| < 2^18): three-constant Cody-Waite
+// reduction to [-pi, pi] (the first product is exact for |k| < 2^16), then the SFU
+// approximations, whose absolute error on that interval is below 1e-6.
+__device__ __forceinline__ void sincos_reduced(float x, float& sn, float& cs) {
+  const float k = rintf(x * 0.15915494309189535f);
+  float r = fmaf(k, -6.28125f, x);
+  r = fmaf(k, -1.9350051879882812e-3f, r);
+  r = fmaf(k, -3.019916050561733e-7f, r);
+  sn = __sinf(r);
+  cs = __cosf(r);
+}
+
 template <typename T> struct TypeTraits;
 template <> struct TypeTraits<__nv_bfloat16> {
   static constexpr uint32_t kFmt = 1;
@@ -266,6 +282,11 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (threadIdx.x >= 128 && threadIdx.x < 256) {   // running maxima start at -inf
     float* m_s = reinterpret_cast<float*>(sm + OFF_M);
     if (threadIdx.x - 128 < 64) m_s[threadIdx.x - 128] = -CUDART_INF_F;
+  }
+  if (threadIdx.x >= 256 && threadIdx.x < 320) {
+    const int j = threadIdx.x - 256;
+    reinterpret_cast<float*>(sm + OFF_FREQ)[j] =
+        a.inv_freq ? a.inv_freq[j] : 1.0f / powf(a.theta, (float)(2 * j) / (float)D);
   }
   tc_fence_before();
   __syncthreads();
@@ -366,20 +387,41 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     float* alpha_s = reinterpret_cast<float*>(sm + OFF_ALPHA);
     float* m_s = reinterpret_cast<float*>(sm + OFF_M);
     const T* qg = static_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
+    const float* freq_s = reinterpret_cast<const float*>(sm + OFF_FREQ);
     int abuf = 0, pbuf = 0, par = 0;
     uint32_t aphase = 0, pphase = 0;
+    // The chunk's queries (2 KV heads x G heads x 128 dims) are fetched one chunk ahead into
+    // registers, 8 elements per 128-bit load, so their L2 latency hides under the previous chunk.
+    constexpr int QV = (2 * G * D) / (128 * 8);
+    uint4 qpre[QV];
+    auto q_fetch = [&](int c) {
+#pragma unroll
+      for (int v = 0; v < QV; ++v) {
+        const int idx = (v * 128 + et) * 8;
+        const int hh = idx / (G * D), g = (idx / D) % G, d = idx % D;
+        qpre[v] = *reinterpret_cast<const uint4*>(qg + (int64_t)((2 * c + hh) * G + g) * a.q_sh + d);
+      }
+    };
+    q_fetch(0);
     for (int tile = tile_begin; tile < tile_end; ++tile) {
       const int tok = tile * TILE_M + et;
       const bool valid = tok < a.kv_len;
-      const float4* tab = reinterpret_cast<const float4*>(a.table + (int64_t)min(tok, a.kv_len - 1) * 64);
+      const float pos_f = (float)(a.pos_offset + tok);
       for (int c = 0; c < NCH; ++c) {
         // ---- stage this chunk's queries: q_s[hh][j][g][{j, j+64}] = q * scale -----------------
         if (epilogue_sync_aborted(abort_flag)) goto epi_done;
-        for (int idx = et; idx < 2 * G * D; idx += 128) {
-          const int hh = idx / (G * D), g = (idx / D) % G, d = idx % D;
-          const float v = TypeTraits<T>::to_f(qg[(int64_t)((2 * c + hh) * G + g) * a.q_sh + d]) * a.q_scale;
-          q_s[((hh * 64 + (d & 63)) * G + g) * 2 + (d >> 6)] = v;
+#pragma unroll
+        for (int v = 0; v < QV; ++v) {
+          const int idx = (v * 128 + et) * 8;
+          const int hh = idx / (G * D), g = (idx / D) % G, d0 = idx % D;
+          const T* e8 = reinterpret_cast<const T*>(&qpre[v]);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int d = d0 + e;
+            q_s[((hh * 64 + (d & 63)) * G + g) * 2 + (d >> 6)] = TypeTraits<T>::to_f(e8[e]) * a.q_scale;
+          }
         }
+        q_fetch((c + 1) % NCH);
         float m_old[2 * G];
         if (!LOGITS_ONLY) {
 #pragma unroll
@@ -394,9 +436,10 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int i = 0; i < 2 * G; ++i) s[i] = 0.f;
 #pragma unroll 1
         for (int jb = 0; jb < 4; ++jb) {
-          float4 cs[8];
+          // rotation of this token for frequencies jb*16 .. jb*16+15, shared by both KV heads
+          float cs[16], sn[16];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) cs[i] = __ldg(tab + jb * 8 + i);
+          for (int i = 0; i < 16; ++i) sincos_reduced(__fmul_rn(pos_f, freq_s[jb * 16 + i]), sn[i], cs[i]);
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
             uint32_t x0[16], x1[16];
@@ -406,11 +449,9 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float cc = (i & 1) ? cs[i >> 1].z : cs[i >> 1].x;
-              const float sn = (i & 1) ? cs[i >> 1].w : cs[i >> 1].y;
               const float k0 = __uint_as_float(x0[i]), k1 = __uint_as_float(x1[i]);
-              const float r0 = k0 * cc - k1 * sn;
-              const float r1 = k1 * cc + k0 * sn;
+              const float r0 = k0 * cs[i] - k1 * sn[i];
+              const float r1 = k1 * cs[i] + k0 * sn[i];
               const float2* qp = reinterpret_cast<const float2*>(q_s + ((hh * 64 + jb * 16 + i) * G) * 2);
 #pragma unroll
               for (int g = 0; g < G; ++g) {
@@ -657,6 +698,8 @@ bool recon_tc_supported(const xkv_decode_params& p) {
   if (G != 4 && G != 8) return false;
   if (p.k_rank < BK || p.k_rank % BK != 0) return false;
   if (p.tail_dim != 0 || p.logit_cap > 0.f) return false;
+  if (p.rope_table) return false;   // caller-made tables go through the portable kernel
+  if (p.q_sh % 8 != 0 || (p.batch > 1 && p.q_sb % 8 != 0)) return false;
   if (p.kp_sd != 1 || !aligned16(p.k) || !aligned16(p.k_proj) || !aligned16(p.q)) return false;
   if (!stride_ok(p.k_sl) || (p.batch > 1 && !stride_ok(p.k_sb))) return false;
   if (!stride_ok(p.kp_sr) || !stride_ok(p.kp_sh)) return false;
@@ -685,7 +728,6 @@ bool recon_tc_plan(const xkv_decode_params& p, ReconTcPlan* pl) {
   pl->tiles_per_split = tiles;   // tiles per batch row; the kernel cuts [s*T/S, (s+1)*T/S)
   size_t off = 256;              // status words
   pl->off_table = off;
-  if (!p.rope_table) off += align_up((size_t)p.kv_len * (D / 2) * sizeof(float2), 256);
   pl->off_partial = off;
   const bool lo = (p.flags & XKV_FLAG_LOGITS_ONLY) != 0;
   if (!lo) off += align_up((size_t)p.batch * p.num_heads * best_s * D * sizeof(float), 256);
@@ -729,20 +771,13 @@ int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& pl, void* ws,
 
   int* status = reinterpret_cast<int*>(w);
   clear_status_kernel<<<1, 32, 0, st>>>(status);
-  const float2* table = reinterpret_cast<const float2*>(p.rope_table);
-  if (!table) {
-    float* tb = reinterpret_cast<float*>(w + pl.off_table);
-    int rc = launch_rope_table(tb, p.kv_len, D / 2, p.pos_offset, p.theta, p.inv_freq, st);
-    if (rc != XKV_OK) return rc;
-    table = reinterpret_cast<const float2*>(tb);
-  }
 
   Args a;
   a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = p.num_heads; a.rank = p.k_rank;
   a.num_splits = pl.num_splits; a.tiles_per_row = pl.tiles_per_split;
   a.q_scale = lo ? p.sm_scale : p.sm_scale * 1.4426950408889634f;
   a.q = p.q; a.q_sb = p.q_sb; a.q_sh = p.q_sh;
-  a.table = table;
+  a.inv_freq = p.inv_freq; a.theta = p.theta; a.pos_offset = p.pos_offset;
   a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
   a.lse = reinterpret_cast<float*>(w + pl.off_lse);
   a.logits = p.logits; a.lg_sb = p.lg_sb; a.lg_sh = p.lg_sh;
