@@ -124,6 +124,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   *abort_flag = 1;
   return false;
 }
+#ifdef XKV_TC_PROFILE
+// Debug build only: cycles spent in each kind of wait, summed over CTAs into status[8 + slot].
+#define XKV_PROF_WAIT_L(slot, leader, expr)                                          \
+  [&]() {                                                                            \
+    const long long t0_ = clock64();                                                 \
+    const bool r_ = (expr);                                                          \
+    if (leader)                                                                      \
+      atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + (slot),        \
+                (unsigned long long)(clock64() - t0_));                              \
+    return r_;                                                                       \
+  }()
+#else
+#define XKV_PROF_WAIT_L(slot, leader, expr) (expr)
+#endif
+#define XKV_PROF_WAIT(slot, expr) XKV_PROF_WAIT_L(slot, true, expr)
+
 // Barrier over the 128 epilogue threads that also agrees on the abort flag, so that either all of
 // them leave or none does (a thread that left alone would strand the rest at the next barrier).
 __device__ __forceinline__ bool epilogue_sync_aborted(volatile int* abort_flag) {
@@ -292,6 +308,9 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+#ifdef XKV_TC_PROFILE
+  const long long t_start_ = clock64();
+#endif
 
   if (warp == 0) {
     // =========================== operand producer =============================================
@@ -302,7 +321,7 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (int tile = tile_begin; tile < tile_end; ++tile) {
         for (int c = 0; c < NCH; ++c) {
           for (int kb = 0; kb < KB; ++kb) {
-            if (!mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag)) {
+            if (!XKV_PROF_WAIT(0, mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag))) {
               report(a.status, XKV_ERR_TIMEOUT, 0, tile, c, kb);
               goto producer_done;
             }
@@ -328,14 +347,14 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t phase = 0, aphase = 0;
       for (int tile = tile_begin; tile < tile_end; ++tile) {
         for (int c = 0; c < NCH; ++c) {
-          if (!mbar_wait(bar_tempty(abuf), aphase ^ 1u, abort_flag)) {
+          if (!XKV_PROF_WAIT(1, mbar_wait(bar_tempty(abuf), aphase ^ 1u, abort_flag))) {
             report(a.status, XKV_ERR_TIMEOUT, 1, tile, c, -1);
             goto mma_done;
           }
           tc_fence_after();
           const uint32_t tacc = tmem_base + (uint32_t)abuf * 256u;
           for (int kb = 0; kb < KB; ++kb) {
-            if (!mbar_wait(bar_full(stage), phase, abort_flag)) {
+            if (!XKV_PROF_WAIT(2, mbar_wait(bar_full(stage), phase, abort_flag))) {
               report(a.status, XKV_ERR_TIMEOUT, 1, tile, c, kb);
               goto mma_done;
             }
@@ -364,7 +383,7 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t ph = 0;
       for (int tile = tile_begin; tile < tile_end; ++tile) {
         for (int kvh = 0; kvh < KVH; ++kvh) {
-          if (!mbar_wait(bar_vempty(slot), ph ^ 1u, abort_flag)) {
+          if (!XKV_PROF_WAIT(3, mbar_wait(bar_vempty(slot), ph ^ 1u, abort_flag))) {
             report(a.status, XKV_ERR_TIMEOUT, 2, tile, kvh, -1);
             goto vprod_done;
           }
@@ -428,7 +447,7 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           for (int i = 0; i < 2 * G; ++i) m_old[i] = m_s[c * 2 * G + i];
         }
         if (epilogue_sync_aborted(abort_flag)) goto epi_done;
-        if (!mbar_wait(bar_tfull(abuf), aphase, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 4, tile, c, 0);
+        if (!XKV_PROF_WAIT_L(4, et == 0, mbar_wait(bar_tfull(abuf), aphase, abort_flag))) report(a.status, XKV_ERR_TIMEOUT, 4, tile, c, 0);
         tc_fence_after();
 
         float s[2 * G];
@@ -492,7 +511,7 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             m_new[i] = mx;
           }
           par ^= 1;
-          if (!mbar_wait(bar_pempty(pbuf), pphase ^ 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 4, tile, c, 1);
+          if (!XKV_PROF_WAIT_L(5, et == 0, mbar_wait(bar_pempty(pbuf), pphase ^ 1u, abort_flag))) report(a.status, XKV_ERR_TIMEOUT, 4, tile, c, 1);
           T* p_s = reinterpret_cast<T*>(sm + OFF_P + pbuf * P_BUF);
 #pragma unroll
           for (int i = 0; i < 2 * G; ++i)
@@ -533,7 +552,7 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (int tile = tile_begin; tile < tile_end && alive; ++tile) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
-          bool ok = mbar_wait(bar_pfull(pbuf), pph, abort_flag);
+          bool ok = XKV_PROF_WAIT_L(6, threadIdx.x == 256, mbar_wait(bar_pfull(pbuf), pph, abort_flag));
           if (!__all_sync(0xffffffffu, ok)) {
             if (lane == 0) report(a.status, XKV_ERR_TIMEOUT, 8, tile, c, 0);
             alive = false;
@@ -543,7 +562,7 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
             const int kvh = 2 * c + hh;
-            ok = mbar_wait(bar_vfull(slot), vph, abort_flag);
+            ok = XKV_PROF_WAIT_L(7, threadIdx.x == 256, mbar_wait(bar_vfull(slot), vph, abort_flag));
             if (!__all_sync(0xffffffffu, ok)) {
               if (lane == 0) report(a.status, XKV_ERR_TIMEOUT, 8, tile, c, 1 + hh);
               alive = false;
@@ -626,6 +645,14 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 
   // =========================== common exit =====================================================
+#ifdef XKV_TC_PROFILE
+  if (threadIdx.x == 128)   // epilogue leader: time from start until the epilogue has finished
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 8, (unsigned long long)(clock64() - t_start_));
+  if (threadIdx.x == 32)    // MMA issuer
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 9, (unsigned long long)(clock64() - t_start_));
+  if (threadIdx.x == 256)   // P.V leader
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 10, (unsigned long long)(clock64() - t_start_));
+#endif
   __syncwarp();
   tc_fence_before();
   __syncthreads();
@@ -641,7 +668,7 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 __global__ void clear_status_kernel(int* status) {
-  if (threadIdx.x < 8) status[threadIdx.x] = 0;
+  if (threadIdx.x < 64) status[threadIdx.x] = 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -770,7 +797,7 @@ int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& pl, void* ws,
   }
 
   int* status = reinterpret_cast<int*>(w);
-  clear_status_kernel<<<1, 32, 0, st>>>(status);
+  clear_status_kernel<<<1, 64, 0, st>>>(status);
 
   Args a;
   a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = p.num_heads; a.rank = p.k_rank;
