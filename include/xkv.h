@@ -40,7 +40,8 @@ typedef enum xkv_status {
   XKV_ERR_WORKSPACE = -4,   /* workspace null or too small                                   */
   XKV_ERR_LAUNCH = -5,      /* CUDA reported an error at launch                              */
   XKV_ERR_TIMEOUT = -6,     /* a bounded device-side wait expired (read from the status word) */
-  XKV_ERR_NO_DEVICE = -7    /* no usable sm_100 device / driver entry point                  */
+  XKV_ERR_NO_DEVICE = -7,   /* no usable sm_100 device / driver entry point                  */
+  XKV_ERR_SCRATCH_LIMIT = -8 /* xkv_decode_builtin_scratch(): request exceeds the built-in array */
 } xkv_status;
 
 typedef enum xkv_dtype { XKV_F32 = 0, XKV_BF16 = 1, XKV_F16 = 2 } xkv_dtype;
@@ -124,6 +125,32 @@ XKV_API size_t xkv_decode_workspace_bytes(const xkv_decode_params* p);
  * cudaStream_t passed as void*.  Replaces the device work of every function below.
  */
 XKV_API int xkv_decode(const xkv_decode_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Decode attention for callers that cannot allocate device memory.
+ *
+ * Some hosts of this library never get to call cudaMalloc: a plugin running inside a server
+ * whose memory pool was sized and frozen at start-up, a real-time loop that must not touch the
+ * allocator, a process whose device memory is entirely owned by another runtime.  For them this
+ * entry point runs the same portable split-KV kernels as xkv_decode() (every score / value
+ * mode and dtype) but takes its scratch from an array compiled into the library instead of a
+ * caller workspace.  It calls no cudaMalloc / cudaFree and no allocating library routine; the
+ * caller still passes inputs and outputs.  It has no counterpart in the reference, whose
+ * wrappers allocate their intermediate buffers with torch on every call.
+ *
+ *  - The array is XKV_BUILTIN_SCRATCH_BYTES (8 MiB) of device memory on every GPU that loads
+ *    the library, held until the process exits.  A request whose split-KV partials need more
+ *    returns XKV_ERR_SCRATCH_LIMIT and launches nothing (lower num_splits or the batch, or use
+ *    xkv_decode() with a workspace).  The tensor-core kernels are not used on this path.
+ *  - The first call on each device resolves the array's device address (cudaGetSymbolAddress,
+ *    with that device current).  Make that first call outside any stream capture.
+ *  - All calls on one device share the one array, which keeps whatever the last call left in
+ *    it; every call rewrites what it later reads, so stale contents are harmless, but two
+ *    calls that overlap on the GPU (different streams, or concurrent host threads) race on
+ *    it.  Serialise them.
+ */
+#define XKV_BUILTIN_SCRATCH_BYTES (8u << 20)
+XKV_API int xkv_decode_builtin_scratch(const xkv_decode_params* p, void* stream);
 
 /*
  * Synchronises `stream` and reads back the status words the last xkv_decode() on this workspace

@@ -22,7 +22,7 @@ _DTYPES = {torch.float32: XKV_F32, torch.bfloat16: XKV_BF16, torch.float16: XKV_
 
 EXPORTS = [
     "xkv_version", "xkv_decode_params_size", "xkv_strerror", "xkv_decode_plan", "xkv_decode_workspace_bytes", "xkv_decode",
-    "xkv_workspace_status",
+    "xkv_workspace_status", "xkv_decode_builtin_scratch",
     "xkv_dense_decode", "xkv_absorbed_decode", "xkv_recon_rope_decode", "xkv_qab_logits",
     "xkv_mla_decode", "xkv_group_decode_workspace_bytes", "xkv_group_decode", "xkv_merge",
     "xkv_rope_table",
@@ -100,6 +100,8 @@ def load():
         lib.xkv_rope_table.restype = C.c_int
         lib.xkv_rope_table.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
         lib.xkv_decode_params_size.restype = C.c_size_t
+        lib.xkv_decode_builtin_scratch.restype = C.c_int
+        lib.xkv_decode_builtin_scratch.argtypes = [C.POINTER(DecodeParams), C.c_void_p]
         lib.xkv_workspace_status.restype = C.c_int
         lib.xkv_workspace_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
         if lib.xkv_version() != 1:
@@ -118,7 +120,7 @@ def check(rc: int, what: str):
     if rc == 0:
         return
     msg = f"{what}: {strerror(rc)} (status {rc})"
-    if rc in (-1, -2, -3):
+    if rc in (-1, -2, -3, -8):
         raise ValueError(msg)
     raise RuntimeError(msg)
 
@@ -188,6 +190,15 @@ def last_status(device: torch.device):
     detail = (C.c_int32 * 8)()
     rc = load().xkv_workspace_status(buf.data_ptr(), key[1], detail)
     return rc, list(detail)
+
+
+BUILTIN_SCRATCH_BYTES = 8 << 20
+
+
+def run_decode_builtin_scratch(params: DecodeParams, device: torch.device):
+    """Launch through xkv_decode_builtin_scratch: no workspace tensor, no allocation."""
+    rc = load().xkv_decode_builtin_scratch(C.byref(params), torch.cuda.current_stream(device).cuda_stream)
+    check(rc, "xkv_decode_builtin_scratch")
 
 
 def plan_name(params: DecodeParams):

@@ -85,6 +85,8 @@ const char* xkv_strerror(int status) {
     case XKV_ERR_LAUNCH: return "CUDA launch failed";
     case XKV_ERR_TIMEOUT: return "bounded device-side wait expired";
     case XKV_ERR_NO_DEVICE: return "no usable sm_100 device or driver entry point";
+    case XKV_ERR_SCRATCH_LIMIT:
+      return "request needs more scratch than the library's built-in array holds; use xkv_decode() with a workspace";
     default: return "unknown status";
   }
 }
@@ -127,6 +129,14 @@ int xkv_decode(const xkv_decode_params* p, void* ws, size_t ws_bytes, void* stre
     default:
       return XKV_ERR_UNSUPPORTED;
   }
+}
+
+int xkv_decode_builtin_scratch(const xkv_decode_params* p, void* stream) {
+  int rc = validate(p);
+  if (rc != XKV_OK) return rc;
+  GenericPlan gp;
+  if (!generic_plan(*p, &gp)) return XKV_ERR_UNSUPPORTED;
+  return generic_decode_builtin_scratch(*p, gp, static_cast<cudaStream_t>(stream));
 }
 
 int xkv_dense_decode(const xkv_decode_params* p, void* ws, size_t n, void* st) {

@@ -13,6 +13,7 @@
 //                            are run-to-run identical), then the optional value projection.
 #include "xkv_internal.h"
 #include <math_constants.h>
+#include <mutex>
 
 namespace xkv {
 namespace {
@@ -450,6 +451,41 @@ int generic_decode(const xkv_decode_params& p, const GenericPlan& pl, void* ws, 
     case XKV_F16: return run_generic<__half>(p, pl, ws, st);
     default: return XKV_ERR_BAD_ARG;
   }
+}
+
+// ---- built-in scratch for callers that cannot allocate device memory ---------------------------
+// One fixed array per device that loads the library, resident until the process exits.  In host
+// code the symbol below is only a handle; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_builtin_scratch[XKV_BUILTIN_SCRATCH_BYTES];
+
+int generic_decode_builtin_scratch(const xkv_decode_params& p, const GenericPlan& pl, cudaStream_t st) {
+  if (pl.total_bytes > (size_t)XKV_BUILTIN_SCRATCH_BYTES) return XKV_ERR_SCRATCH_LIMIT;
+  constexpr int kMaxDevices = 64;
+  static void* dev_ptr[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return XKV_ERR_NO_DEVICE;
+  }
+  void* ptr = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!dev_ptr[dev]) {
+      // first call on this device: resolve the array's device address (no allocation happens)
+      void* sym = nullptr;
+      if (cudaGetSymbolAddress(&sym, g_builtin_scratch) != cudaSuccess || !sym) {
+        cudaGetLastError();
+        return XKV_ERR_NO_DEVICE;
+      }
+      dev_ptr[dev] = sym;
+    }
+    ptr = dev_ptr[dev];
+  }
+  // Every region of the scratch that a kernel reads is written earlier in the same call: the
+  // status words and q_eff by the first kernel, each (batch, head, split) partial and its
+  // log-sum-exp by the split-KV pass.  Nothing relies on the previous call's contents.
+  return generic_decode(p, pl, ptr, st);
 }
 
 int launch_merge(const float* partial_o, const float* lse, void* out, int dtype, int batch, int num_heads,

@@ -30,6 +30,7 @@ struct GenericPlan {
 };
 bool generic_plan(const xkv_decode_params& p, GenericPlan* plan);
 int generic_decode(const xkv_decode_params& p, const GenericPlan& plan, void* ws, cudaStream_t st);
+int generic_decode_builtin_scratch(const xkv_decode_params& p, const GenericPlan& plan, cudaStream_t st);
 int launch_merge(const float* partial_o, const float* lse, void* out, int dtype, int batch,
                  int num_heads, int num_splits, int acc_dim, int value_dim, const void* v_proj,
                  int v_proj_heads, int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd,

@@ -173,6 +173,16 @@ def decode(*, entry: str = "xkv_decode", **kw):
     return result
 
 
+def decode_builtin_scratch(**kw):
+    """Same call as decode(), for hosts that must not allocate device memory: the library's
+    built-in scratch array replaces the workspace (see xkv_decode_builtin_scratch in
+    include/xkv.h for the size limit and the sharing rules).  The output tensor must be passed
+    in (`out=` or, for logits, it is still created here by the caller's allocator)."""
+    p, result = build_params(**kw)
+    _C.run_decode_builtin_scratch(p, kw["q"].device)
+    return result
+
+
 def plan(**kw):
     """Name of the kernel family the library would run for these arguments."""
     p, _ = build_params(**kw)
