@@ -206,7 +206,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
 // reduction to [-pi, pi] (the first product is exact for |k| < 2^16), then the SFU
 // approximations, whose absolute error on that interval is below 1e-6.
 __device__ __forceinline__ void sincos_reduced(float x, float& sn, float& cs) {
-  const float k = rintf(x * 0.15915494309189535f);
+  // round to nearest integer on the FMA pipe: |x / 2pi| < 2^22 here, so adding and removing
+  // 1.5 * 2^23 leaves the rounded value (the conversion instruction shares the busy SFU pipe)
+  const float k = __fadd_rn(__fadd_rn(x * 0.15915494309189535f, 12582912.0f), -12582912.0f);
   float r = fmaf(k, -6.28125f, x);
   r = fmaf(k, -1.9350051879882812e-3f, r);
   r = fmaf(k, -3.019916050561733e-7f, r);
