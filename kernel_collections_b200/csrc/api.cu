@@ -168,9 +168,10 @@ int xkv_mla_decode(const xkv_decode_params* p, void* ws, size_t n, void* st) {
   return rc != XKV_OK ? rc : xkv_decode(p, ws, n, st);
 }
 
-// Group decode: the layers share the key latent.  Each layer runs the single-layer path on the
-// shared workspace, back to back on the stream, so the latent tiles of layer i+1 are served
-// from L2 where the group's latent fits.
+// Group decode: the layers share the key latent.  Groups the tensor-core kernel covers run as ONE
+// launch whose CTAs for the different layers of a (split, batch row) are scheduled together, so a
+// latent tile is fetched from HBM once and served from L2 to the other layers.  Anything else
+// runs layer by layer on the shared workspace.
 static int group_check(const xkv_decode_params* layers, int n) {
   if (!layers || n <= 0) return XKV_ERR_BAD_ARG;
   for (int i = 0; i < n; ++i) {
@@ -190,6 +191,8 @@ static int group_check(const xkv_decode_params* layers, int n) {
 
 size_t xkv_group_decode_workspace_bytes(const xkv_decode_params* layers, int n) {
   if (group_check(layers, n) != XKV_OK) return 0;
+  ReconTcPlan rp;
+  if (recon_tc_group_supported(layers, n) && recon_tc_group_plan(layers, n, &rp)) return rp.total_bytes;
   size_t mx = 0;
   for (int i = 0; i < n; ++i) {
     size_t b = xkv_decode_workspace_bytes(&layers[i]);
@@ -202,6 +205,11 @@ size_t xkv_group_decode_workspace_bytes(const xkv_decode_params* layers, int n) 
 int xkv_group_decode(const xkv_decode_params* layers, int n, void* ws, size_t ws_bytes, void* stream) {
   int rc = group_check(layers, n);
   if (rc != XKV_OK) return rc;
+  ReconTcPlan rp;
+  if (recon_tc_group_supported(layers, n) && recon_tc_group_plan(layers, n, &rp)) {
+    if (!ws || ws_bytes < rp.total_bytes) return XKV_ERR_WORKSPACE;
+    return recon_tc_group_decode(layers, n, rp, ws, static_cast<cudaStream_t>(stream));
+  }
   for (int i = 0; i < n; ++i) {
     rc = xkv_decode(&layers[i], ws, ws_bytes, stream);
     if (rc != XKV_OK) return rc;

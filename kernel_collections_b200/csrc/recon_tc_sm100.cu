@@ -61,17 +61,28 @@ static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
 // status words in the workspace
 enum { ST_CODE = 0, ST_ROLE = 1, ST_TILE = 2, ST_CHUNK = 3, ST_EXTRA = 4 };
 
+constexpr int MAX_LAYERS = 8;   // layers of one cross-layer group served by a single launch
+
+// Tensor maps of one launch: the key latent is shared by all layers, projections and values are
+// per layer.
+struct TensorMaps {
+  CUtensorMap a;
+  CUtensorMap b[MAX_LAYERS];
+  CUtensorMap v[MAX_LAYERS];
+};
+
 struct Args {
+  int num_layers;
   int batch, kv_len, num_heads, rank;
   int num_splits, tiles_per_row;
   float q_scale;
-  const void* q;
+  const void* q[MAX_LAYERS];
   int64_t q_sb, q_sh;
   const float* inv_freq; // 64 RoPE frequencies (device) or NULL -> theta
   float theta;
   int pos_offset;
-  float* partial_o;      // [batch][H][splits][128]
-  float* lse;            // [batch][H][splits]
+  float* partial_o;      // [layer][batch][H][splits][128]
+  float* lse;            // [layer][batch][H][splits]
   void* logits;
   int64_t lg_sb, lg_sh;
   int* status;
@@ -254,15 +265,21 @@ __device__ __forceinline__ void report(int* status, int code, int role, int tile
 // ---------------------------------------------------------------------------------------------
 template <typename T, int G, bool LOGITS_ONLY>
 __global__ void __launch_bounds__(NTHREADS, 1)
-recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const __grid_constant__ CUtensorMap tmV, const Args a) {
+recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int split = blockIdx.x, b = blockIdx.y;
+  // The layer index varies fastest over the grid: the CTAs of one (split, batch row) that serve
+  // the layers of a group are scheduled together and stream the same latent tiles, which are then
+  // read from HBM once and served from L2 to the other layers.
+  const int layer = blockIdx.x % a.num_layers, split = blockIdx.x / a.num_layers, b = blockIdx.y;
+  const CUtensorMap* tmA = &maps.a;
+  const CUtensorMap* tmB = &maps.b[layer];
+  const CUtensorMap* tmV = &maps.v[layer];
+  const int64_t row = (int64_t)layer * a.batch + b;   // row of the partial / lse buffers
   const int tile_begin = (int)(((int64_t)split * a.tiles_per_row) / a.num_splits);
   const int tile_end = (int)(((int64_t)(split + 1) * a.tiles_per_row) / a.num_splits);
   const int KB = a.rank / BK;
@@ -329,10 +346,10 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
             mbar_expect_tx(bar_full(stage), STAGE_BYTES);
             const uint32_t sa = base + OFF_STAGE + stage * STAGE_BYTES;
-            tma_load_3d(sa, &tmA, kb * BK, tile * TILE_M, b, bar_full(stage));
+            tma_load_3d(sa, tmA, kb * BK, tile * TILE_M, b, bar_full(stage));
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              tma_load_4d(sa + A_BYTES + i * B_BOX, &tmB, (i & 1) * 64, kb * BK, 2 * c + (i >> 1), bb, bar_full(stage));
+              tma_load_4d(sa + A_BYTES + i * B_BOX, tmB, (i & 1) * 64, kb * BK, 2 * c + (i >> 1), bb, bar_full(stage));
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
         }
@@ -391,8 +408,8 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           mbar_expect_tx(bar_vfull(slot), V_SLOT);
           const uint32_t sv = base + OFF_V + slot * V_SLOT;
-          tma_load_4d(sv, &tmV, 0, kvh, tile * TILE_M, b, bar_vfull(slot));
-          tma_load_4d(sv + V_SLOT / 2, &tmV, 64, kvh, tile * TILE_M, b, bar_vfull(slot));
+          tma_load_4d(sv, tmV, 0, kvh, tile * TILE_M, b, bar_vfull(slot));
+          tma_load_4d(sv + V_SLOT / 2, tmV, 64, kvh, tile * TILE_M, b, bar_vfull(slot));
           if (++slot == V_SLOTS) { slot = 0; ph ^= 1u; }
         }
       }
@@ -407,7 +424,7 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     float* wmax_s = reinterpret_cast<float*>(sm + OFF_WMAX);
     float* alpha_s = reinterpret_cast<float*>(sm + OFF_ALPHA);
     float* m_s = reinterpret_cast<float*>(sm + OFF_M);
-    const T* qg = static_cast<const T*>(a.q) + (int64_t)b * a.q_sb;
+    const T* qg = static_cast<const T*>(a.q[layer]) + (int64_t)b * a.q_sb;
     const float* freq_s = reinterpret_cast<const float*>(sm + OFF_FREQ);
     int abuf = 0, pbuf = 0, par = 0;
     uint32_t aphase = 0, pphase = 0;
@@ -629,7 +646,7 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               const int h = kvh * G + hd;
               const float l = lacc[kvh][n];
               const float inv = l > 0.f ? 1.f / l : 0.f;
-              float* po = a.partial_o + (((int64_t)b * H + h) * a.num_splits + split) * D;
+              float* po = a.partial_o + ((row * H + h) * a.num_splits + split) * D;
 #pragma unroll
               for (int mt = 0; mt < 2; ++mt) {
                 const int dim = pw * 32 + mt * 16 + g;
@@ -637,7 +654,7 @@ recon_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 po[dim + 8] = acc[kvh][mt][2 + n] * inv;
               }
               if (pw == 0 && g == 0)
-                a.lse[((int64_t)b * H + h) * a.num_splits + split] =
+                a.lse[(row * H + h) * a.num_splits + split] =
                     l > 0.f ? (m_s[h] + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
             }
           }
@@ -707,13 +724,13 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 bool stride_ok(int64_t elems) { return elems > 0 && (elems * 2) % 16 == 0; }
 
 template <typename T, int G, bool LO>
-int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tV, const Args& args, cudaStream_t st) {
+int launch(const TensorMaps& maps, const Args& args, cudaStream_t st) {
   auto kern = recon_tc_kernel<T, G, LO>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
     cudaGetLastError();
     return XKV_ERR_LAUNCH;
   }
-  kern<<<dim3(args.num_splits, args.batch), NTHREADS, SMEM_BYTES, st>>>(tA, tB, tV, args);
+  kern<<<dim3(args.num_splits * args.num_layers, args.batch), NTHREADS, SMEM_BYTES, st>>>(maps, args);
   return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
 }
 
@@ -742,70 +759,113 @@ bool recon_tc_supported(const xkv_decode_params& p) {
   return true;
 }
 
-bool recon_tc_plan(const xkv_decode_params& p, ReconTcPlan* pl) {
-  const int tiles = ceil_div(p.kv_len, TILE_M);
+// Split count for `rows` independent (layer, batch row) streams of `tiles` tiles each.
+static int choose_splits(int rows, int tiles) {
   const int sms = device_sm_count();
   int best_s = 1;
   int64_t best_cost = -1;
   const int max_s = tiles < 64 ? tiles : 64;
   for (int s = 1; s <= max_s; ++s) {
-    const int64_t waves = ceil_div(p.batch * s, sms);
+    const int64_t waves = ceil_div(rows * s, sms);
     const int64_t cost = waves * ceil_div(tiles, s);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = s; }
   }
-  pl->num_splits = best_s;
+  return best_s;
+}
+
+static bool plan_layers(const xkv_decode_params& p, int num_layers, ReconTcPlan* pl) {
+  const int tiles = ceil_div(p.kv_len, TILE_M);
+  pl->num_splits = choose_splits(p.batch * num_layers, tiles);
   pl->tiles_per_split = tiles;   // tiles per batch row; the kernel cuts [s*T/S, (s+1)*T/S)
   size_t off = 256;              // status words
   pl->off_table = off;
   pl->off_partial = off;
   const bool lo = (p.flags & XKV_FLAG_LOGITS_ONLY) != 0;
-  if (!lo) off += align_up((size_t)p.batch * p.num_heads * best_s * D * sizeof(float), 256);
+  const size_t rows = (size_t)num_layers * p.batch * p.num_heads * pl->num_splits;
+  if (!lo) off += align_up(rows * D * sizeof(float), 256);
   pl->off_lse = off;
-  if (!lo) off += align_up((size_t)p.batch * p.num_heads * best_s * sizeof(float), 256);
+  if (!lo) off += align_up(rows * sizeof(float), 256);
   pl->total_bytes = off;
   return true;
 }
 
-int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& pl, void* ws, cudaStream_t st) {
+bool recon_tc_plan(const xkv_decode_params& p, ReconTcPlan* pl) { return plan_layers(p, 1, pl); }
+
+bool recon_tc_group_supported(const xkv_decode_params* layers, int n) {
+  if (n < 1 || n > MAX_LAYERS) return false;
+  for (int i = 0; i < n; ++i) {
+    const xkv_decode_params &a = layers[0], &b = layers[i];
+    if (!recon_tc_supported(b) || (b.flags & (XKV_FLAG_LOGITS_ONLY | XKV_FLAG_FORCE_GENERIC))) return false;
+    if (a.q_sb != b.q_sb || a.q_sh != b.q_sh || a.sm_scale != b.sm_scale || a.theta != b.theta ||
+        a.pos_offset != b.pos_offset || a.inv_freq != b.inv_freq || a.k != b.k || a.k_sb != b.k_sb ||
+        a.k_sl != b.k_sl || (a.kp_sb != 0) != (b.kp_sb != 0))
+      return false;
+  }
+  return true;
+}
+
+bool recon_tc_group_plan(const xkv_decode_params* layers, int n, ReconTcPlan* pl) {
+  return plan_layers(layers[0], n, pl);
+}
+
+static bool encode_b(CUtensorMap* m, const xkv_decode_params& p, int b_batched) {
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)p.k_rank, (cuuint64_t)KVH, (cuuint64_t)(b_batched ? p.batch : 1)};
+  const int64_t sb = b_batched ? p.kp_sb : (int64_t)KVH * p.k_rank * D * 4;
+  const cuuint64_t strides[3] = {(cuuint64_t)p.kp_sr * 2, (cuuint64_t)p.kp_sh * 2, (cuuint64_t)sb * 2};
+  const cuuint32_t box[4] = {64, BK, 1, 1};
+  return encode(m, p.dtype, 4, p.k_proj, dims, strides, box);
+}
+
+static bool encode_v(CUtensorMap* m, const xkv_decode_params& p) {
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)KVH, (cuuint64_t)p.kv_len, (cuuint64_t)p.batch};
+  const int64_t sb = p.batch > 1 ? p.v_sb : (int64_t)p.kv_len * KVH * D * 4;
+  const cuuint64_t strides[3] = {(cuuint64_t)p.v_sh * 2, (cuuint64_t)p.v_sl * 2, (cuuint64_t)sb * 2};
+  const cuuint32_t box[4] = {64, 1, TILE_M, 1};
+  return encode(m, p.dtype, 4, p.v, dims, strides, box);
+}
+
+int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcPlan& pl, void* ws,
+                          cudaStream_t st) {
+  const xkv_decode_params& p = layers[0];
   char* w = static_cast<char*>(ws);
   if (!aligned16(w)) return XKV_ERR_ALIGN;
   const bool lo = (p.flags & XKV_FLAG_LOGITS_ONLY) != 0;
   const int G = p.num_heads / p.num_kv_heads;
 
-  CUtensorMap tA, tB, tV;
+  TensorMaps maps;
   {
     const cuuint64_t dims[3] = {(cuuint64_t)p.k_rank, (cuuint64_t)p.kv_len, (cuuint64_t)p.batch};
     const int64_t sb = p.batch > 1 ? p.k_sb : (int64_t)p.kv_len * p.k_sl;
     const cuuint64_t strides[2] = {(cuuint64_t)p.k_sl * 2, (cuuint64_t)sb * 2};
     const cuuint32_t box[3] = {BK, TILE_M, 1};
-    if (!encode(&tA, p.dtype, 3, p.k, dims, strides, box)) return XKV_ERR_NO_DEVICE;
+    if (!encode(&maps.a, p.dtype, 3, p.k, dims, strides, box)) return XKV_ERR_NO_DEVICE;
   }
   const int b_batched = (p.kp_sb != 0 && p.batch > 1) ? 1 : 0;
-  {
-    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)p.k_rank, (cuuint64_t)KVH, (cuuint64_t)(b_batched ? p.batch : 1)};
-    const int64_t sb = b_batched ? p.kp_sb : (int64_t)KVH * p.k_rank * D * 4;
-    const cuuint64_t strides[3] = {(cuuint64_t)p.kp_sr * 2, (cuuint64_t)p.kp_sh * 2, (cuuint64_t)sb * 2};
-    const cuuint32_t box[4] = {64, BK, 1, 1};
-    if (!encode(&tB, p.dtype, 4, p.k_proj, dims, strides, box)) return XKV_ERR_NO_DEVICE;
-  }
-  if (!lo) {
-    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)KVH, (cuuint64_t)p.kv_len, (cuuint64_t)p.batch};
-    const int64_t sb = p.batch > 1 ? p.v_sb : (int64_t)p.kv_len * KVH * D * 4;
-    const cuuint64_t strides[3] = {(cuuint64_t)p.v_sh * 2, (cuuint64_t)p.v_sl * 2, (cuuint64_t)sb * 2};
-    const cuuint32_t box[4] = {64, 1, TILE_M, 1};
-    if (!encode(&tV, p.dtype, 4, p.v, dims, strides, box)) return XKV_ERR_NO_DEVICE;
-  } else {
-    tV = tA;
+  for (int i = 0; i < MAX_LAYERS; ++i) {
+    const xkv_decode_params& li = layers[i < n ? i : 0];
+    if (i < n) {
+      if (!encode_b(&maps.b[i], li, b_batched)) return XKV_ERR_NO_DEVICE;
+      if (!lo) {
+        if (!encode_v(&maps.v[i], li)) return XKV_ERR_NO_DEVICE;
+      } else {
+        maps.v[i] = maps.a;
+      }
+    } else {
+      maps.b[i] = maps.b[0];
+      maps.v[i] = maps.v[0];
+    }
   }
 
   int* status = reinterpret_cast<int*>(w);
   clear_status_kernel<<<1, 64, 0, st>>>(status);
 
   Args a;
+  a.num_layers = n;
   a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = p.num_heads; a.rank = p.k_rank;
   a.num_splits = pl.num_splits; a.tiles_per_row = pl.tiles_per_split;
   a.q_scale = lo ? p.sm_scale : p.sm_scale * 1.4426950408889634f;
-  a.q = p.q; a.q_sb = p.q_sb; a.q_sh = p.q_sh;
+  for (int i = 0; i < MAX_LAYERS; ++i) a.q[i] = layers[i < n ? i : 0].q;
+  a.q_sb = p.q_sb; a.q_sh = p.q_sh;
   a.inv_freq = p.inv_freq; a.theta = p.theta; a.pos_offset = p.pos_offset;
   a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
   a.lse = reinterpret_cast<float*>(w + pl.off_lse);
@@ -814,8 +874,7 @@ int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& pl, void* ws,
   a.b_batched = b_batched;
 
   int rc;
-#define XKV_TC(T, GG)                                                        \
-  rc = lo ? launch<T, GG, true>(tA, tB, tV, a, st) : launch<T, GG, false>(tA, tB, tV, a, st)
+#define XKV_TC(T, GG) rc = lo ? launch<T, GG, true>(maps, a, st) : launch<T, GG, false>(maps, a, st)
   if (p.dtype == XKV_BF16) {
     if (G == 4) { XKV_TC(__nv_bfloat16, 4); } else { XKV_TC(__nv_bfloat16, 8); }
   } else {
@@ -824,8 +883,17 @@ int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& pl, void* ws,
 #undef XKV_TC
   if (rc != XKV_OK) return rc;
   if (lo) return XKV_OK;
-  return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, D, D, nullptr, 1,
-                      0, 0, 0, 0, p.o_sb, p.o_sh, st);
+  const size_t layer_rows = (size_t)p.batch * p.num_heads * pl.num_splits;
+  for (int i = 0; i < n; ++i) {
+    rc = launch_merge(a.partial_o + i * layer_rows * D, a.lse + i * layer_rows, layers[i].out, p.dtype, p.batch,
+                      p.num_heads, pl.num_splits, D, D, nullptr, 1, 0, 0, 0, 0, layers[i].o_sb, layers[i].o_sh, st);
+    if (rc != XKV_OK) return rc;
+  }
+  return XKV_OK;
+}
+
+int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& pl, void* ws, cudaStream_t st) {
+  return recon_tc_group_decode(&p, 1, pl, ws, st);
 }
 
 }  // namespace xkv

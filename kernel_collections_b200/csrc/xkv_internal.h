@@ -47,5 +47,10 @@ struct ReconTcPlan {
 bool recon_tc_supported(const xkv_decode_params& p);
 bool recon_tc_plan(const xkv_decode_params& p, ReconTcPlan* plan);
 int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& plan, void* ws, cudaStream_t st);
+// one launch for the layers of a cross-layer group that share the key latent
+bool recon_tc_group_supported(const xkv_decode_params* layers, int n);
+bool recon_tc_group_plan(const xkv_decode_params* layers, int n, ReconTcPlan* plan);
+int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcPlan& plan, void* ws,
+                          cudaStream_t st);
 
 }  // namespace xkv

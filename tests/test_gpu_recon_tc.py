@@ -119,3 +119,30 @@ def test_rope_positions_and_user_table():
     want_off = O.gqa_dense(q, Kr, V.transpose(1, 2))
     got_off = K.recon_rope_decode(qd, Ad, Bd, V.to(DEV).transpose(1, 2), theta=theta, k_position_offset=off)
     assert_close(got_off, want_off, "k_position_offset")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("NL,b,L,R,G", [(4, 2, 700, 128, 4), (3, 1, 2048, 256, 8), (8, 1, 130, 64, 4)])
+def test_group_decode_single_launch(dtype, NL, b, L, R, G):
+    """Cross-layer group on the tensor-core kernel: one launch, layers fastest over the grid; every
+    layer must match its own single-layer result bit for bit and the oracle within tolerance."""
+    theta = 500000.0
+    g = torch.Generator().manual_seed(21)
+    H = KVH * G
+    A = torch.randn(b, L, R, generator=g).to(dtype)
+    qs = [torch.randn(b, H, 1, D, generator=g).to(dtype) for _ in range(NL)]
+    Bs = [(torch.randn(R, KVH * D, generator=g) / R ** 0.5).to(dtype) for _ in range(NL)]
+    Vs = [torch.randn(b, L, KVH, D, generator=g).to(dtype) for _ in range(NL)]
+    Ad = A.to(DEV)
+    qd, Bd, Vd = [x.to(DEV) for x in qs], [x.to(DEV) for x in Bs], [x.to(DEV) for x in Vs]
+    got = K.xkv_group_decode(qd, Ad, Bd, [v.transpose(1, 2) for v in Vd], theta=theta)
+    status_ok()
+    for i in range(NL):
+        want = O.recon_rope_decode(qs[i], A, b4(Bs[i], b), Vs[i].transpose(1, 2), theta)
+        assert_close(got[i], want, f"group layer {i} vs oracle")
+        single = K.recon_rope_decode(qd[i], Ad, Bd[i], Vd[i].transpose(1, 2), theta=theta)
+        # same math, possibly a different split count: equal up to the merge's fp32 rounding
+        assert_close(got[i], single.float().cpu(), f"group layer {i} vs single-layer call", 4e-3, 2e-3)
+    again = K.xkv_group_decode(qd, Ad, Bd, [v.transpose(1, 2) for v in Vd], theta=theta)
+    for i in range(NL):
+        assert torch.equal(got[i], again[i])
