@@ -117,10 +117,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="context 4096 (profiling-sized case, 0.2 GB of inputs)")
     ap.add_argument("--force-generic", action="store_true")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c5"],
+                    help="c2: the headline configuration (default).  c5: one GPU's 16-row shard of the long-context "
+                         "sweep (64 query heads, rank 1024, context 131072); inputs drawn on the device, no e2e leg")
     args = ap.parse_args()
 
     from kernel_collections_b200 import synthetic
     cfg = synthetic.ReconRopeConfig()
+    if args.workload == "c5":
+        cfg = cfg.scaled(name="c5_shard_b16_of_128_L131072_R1024_H64", batch=16, num_heads=64, kv_len=131072, rank=1024)
     if args.small:
         cfg = cfg.scaled(kv_len=4096, name="c2_small_L4096")
     rank = int(os.environ.get("RANK", "0"))
@@ -130,7 +135,7 @@ def main():
               "num_heads": cfg.num_heads, "num_kv_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim,
               "kv_len": cfg.kv_len, "rank": cfg.rank, "rope_theta": cfg.theta, "value": "dense",
               "parallelism": f"batch-shard x{world}" + (" + NCCL all-gather of outputs" if world > 1 else ""),
-              "l2_policy": "inputs (0.8 GB per GPU) exceed the 126 MB L2"}
+              "l2_policy": f"inputs ({cfg.algorithmic_bytes() / 1e9:.2f} GB per GPU) exceed the 126 MB L2"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -161,14 +166,25 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
-    A, B, q, V = synthetic.recon_rope_inputs(cfg, seed=rank)
-    hA, hB, hq, hV = (t.pin_memory() for t in (A, B, q, V))
-    dA, dB, dV = hA.to(dev), hB.to(dev), hV.to(dev)
-    dq = K.rope_query(hq.to(dev), cfg.theta, cfg.kv_len)
-    hq = dq.cpu().pin_memory()          # the rotated query is what a caller hands over each step
-    h2d = sum(t.numel() * t.element_size() for t in (hA, hB, hq, hV))
-    out_host = torch.empty((cfg.batch * world, cfg.num_heads, 1, cfg.head_dim), dtype=cfg.dtype).pin_memory()
-    d2h = out_host.numel() * out_host.element_size()
+    big = args.workload == "c5"          # tens of GB: drawn on the device, e2e leg skipped
+    if big:
+        g = torch.Generator(device=dev).manual_seed(rank)
+        KD = cfg.num_kv_heads * cfg.head_dim
+        dA = torch.randn(cfg.batch, cfg.kv_len, cfg.rank, generator=g, device=dev, dtype=cfg.dtype)
+        dB = (torch.randn(cfg.rank, KD, generator=g, device=dev) / cfg.rank ** 0.5).to(cfg.dtype)
+        dV = torch.randn(cfg.batch, cfg.kv_len, cfg.num_kv_heads, cfg.head_dim, generator=g, device=dev, dtype=cfg.dtype)
+        dq = K.rope_query(torch.randn(cfg.batch, cfg.num_heads, 1, cfg.head_dim, generator=g, device=dev).to(cfg.dtype),
+                          cfg.theta, cfg.kv_len)
+        h2d = d2h = 0
+    else:
+        A, B, q, V = synthetic.recon_rope_inputs(cfg, seed=rank)
+        hA, hB, hq, hV = (t.pin_memory() for t in (A, B, q, V))
+        dA, dB, dV = hA.to(dev), hB.to(dev), hV.to(dev)
+        dq = K.rope_query(hq.to(dev), cfg.theta, cfg.kv_len)
+        hq = dq.cpu().pin_memory()          # the rotated query is what a caller hands over each step
+        h2d = sum(t.numel() * t.element_size() for t in (hA, hB, hq, hV))
+        out_host = torch.empty((cfg.batch * world, cfg.num_heads, 1, cfg.head_dim), dtype=cfg.dtype).pin_memory()
+        d2h = out_host.numel() * out_host.element_size()
 
     def step(a, b_, qq, v):
         o = K.recon_rope_decode(qq, a, b_, v.transpose(1, 2), theta=cfg.theta, force_generic=args.force_generic)
@@ -205,23 +221,25 @@ def main():
 
     # ---- end to end: pinned host -> device, call, result -> host ---------------------------------
     e2e_steps = max(3, min(args.steps, 10))
-    bufs = [torch.empty_like(t, device=dev) for t in (hA, hB, hq, hV)]
+    e2e_ms = float("nan")
+    if not big:
+        bufs = [torch.empty_like(t, device=dev) for t in (hA, hB, hq, hV)]
 
-    def e2e_step():
-        for dst, src in zip(bufs, (hA, hB, hq, hV)):
-            dst.copy_(src, non_blocking=True)
-        o = step(*bufs)
-        out_host.copy_(o, non_blocking=True)
+        def e2e_step():
+            for dst, src in zip(bufs, (hA, hB, hq, hV)):
+                dst.copy_(src, non_blocking=True)
+            o = step(*bufs)
+            out_host.copy_(o, non_blocking=True)
 
-    e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(e2e_steps):
         e2e_step()
-    e1.record(stream)
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record(stream)
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
 
     t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -257,11 +275,11 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": str(cfg.dtype).replace("torch.", ""),
             "data": "synthetic", "config": config, "clocks": clocks,
-            "e2e": {"value": tokens / (e2e_ms / e2e_steps * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+            "e2e": {"value": None if big else tokens / (e2e_ms / e2e_steps * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "note": "all inputs (latent, B, q, dense V) copied from pinned host memory every step"},
             "gpu_launches": launches_per_step * args.steps, "roofline": roof}
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not big:
         v, name, both = cpu_reference_throughput(cfg, max(1, args.cpu_rows), 5, 1)
         line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                                 "dtype": name, "by_dtype": both,

@@ -50,11 +50,20 @@ int validate(const xkv_decode_params* p) {
   return XKV_OK;
 }
 
-enum class Path { kNone, kGeneric, kReconTc };
+enum class Path { kNone, kGeneric, kReconTc, kDenseTc };
 
-Path select(const xkv_decode_params& p, GenericPlan* gp, ReconTcPlan* rp) {
-  if (!(p.flags & XKV_FLAG_FORCE_GENERIC) && recon_tc_supported(p) && recon_tc_plan(p, rp))
-    return Path::kReconTc;
+struct Plans {
+  GenericPlan generic;
+  ReconTcPlan recon;
+  DenseTcPlan dense;
+};
+
+Path select(const xkv_decode_params& p, Plans* pl) {
+  GenericPlan* gp = &pl->generic;
+  if (!(p.flags & XKV_FLAG_FORCE_GENERIC)) {
+    if (recon_tc_supported(p) && recon_tc_plan(p, &pl->recon)) return Path::kReconTc;
+    if (dense_tc_supported(p) && dense_tc_plan(p, &pl->dense)) return Path::kDenseTc;
+  }
   if (generic_plan(p, gp)) return Path::kGeneric;
   return Path::kNone;
 }
@@ -93,10 +102,10 @@ const char* xkv_strerror(int status) {
 
 const char* xkv_decode_plan(const xkv_decode_params* p) {
   if (validate(p) != XKV_OK) return nullptr;
-  GenericPlan gp;
-  ReconTcPlan rp;
-  switch (select(*p, &gp, &rp)) {
+  Plans pl;
+  switch (select(*p, &pl)) {
     case Path::kReconTc: return "recon_tc";
+    case Path::kDenseTc: return "dense_tc";
     case Path::kGeneric: return "generic";
     default: return nullptr;
   }
@@ -104,11 +113,11 @@ const char* xkv_decode_plan(const xkv_decode_params* p) {
 
 size_t xkv_decode_workspace_bytes(const xkv_decode_params* p) {
   if (validate(p) != XKV_OK) return 0;
-  GenericPlan gp;
-  ReconTcPlan rp;
-  switch (select(*p, &gp, &rp)) {
-    case Path::kReconTc: return rp.total_bytes;
-    case Path::kGeneric: return gp.total_bytes;
+  Plans pl;
+  switch (select(*p, &pl)) {
+    case Path::kReconTc: return pl.recon.total_bytes;
+    case Path::kDenseTc: return pl.dense.total_bytes;
+    case Path::kGeneric: return pl.generic.total_bytes;
     default: return 0;
   }
 }
@@ -116,16 +125,18 @@ size_t xkv_decode_workspace_bytes(const xkv_decode_params* p) {
 int xkv_decode(const xkv_decode_params* p, void* ws, size_t ws_bytes, void* stream) {
   int rc = validate(p);
   if (rc != XKV_OK) return rc;
-  GenericPlan gp;
-  ReconTcPlan rp;
+  Plans pl;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  switch (select(*p, &gp, &rp)) {
+  switch (select(*p, &pl)) {
     case Path::kReconTc:
-      if (!ws || ws_bytes < rp.total_bytes) return XKV_ERR_WORKSPACE;
-      return recon_tc_decode(*p, rp, ws, st);
+      if (!ws || ws_bytes < pl.recon.total_bytes) return XKV_ERR_WORKSPACE;
+      return recon_tc_decode(*p, pl.recon, ws, st);
+    case Path::kDenseTc:
+      if (!ws || ws_bytes < pl.dense.total_bytes) return XKV_ERR_WORKSPACE;
+      return dense_tc_decode(*p, pl.dense, ws, st);
     case Path::kGeneric:
-      if (!ws || ws_bytes < gp.total_bytes) return XKV_ERR_WORKSPACE;
-      return generic_decode(*p, gp, ws, st);
+      if (!ws || ws_bytes < pl.generic.total_bytes) return XKV_ERR_WORKSPACE;
+      return generic_decode(*p, pl.generic, ws, st);
     default:
       return XKV_ERR_UNSUPPORTED;
   }

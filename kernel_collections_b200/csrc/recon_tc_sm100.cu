@@ -17,11 +17,10 @@
 // Every mbarrier wait is bounded: on expiry the kernel raises a shared abort flag, records where
 // it gave up in the status words of the workspace, lets every role drain to the common exit,
 // waits for copies in flight, frees its TMEM and returns.  No TMA load uses cluster multicast.
-#include "xkv_internal.h"
-#include <cuda.h>
-#include <math_constants.h>
+#include "sm100_common.cuh"
 
 namespace xkv {
+using namespace sm100;
 namespace {
 
 constexpr int TILE_M = 128;   // tokens per tile == TMEM lanes
@@ -38,8 +37,6 @@ constexpr int V_SLOT = TILE_M * D * 2;         // 32 KB
 constexpr int V_SLOTS = 2;
 constexpr int P_PITCH = TILE_M * 2 + 16;       // bytes per head row of P (padded against bank conflicts)
 constexpr int NTHREADS = 384;
-constexpr uint32_t MAX_POLLS = 1u << 26;
-constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;
 
 constexpr int OFF_STAGE = 0;
 constexpr int OFF_V = OFF_STAGE + STAGES * STAGE_BYTES;          // 147456
@@ -58,8 +55,6 @@ constexpr int SMEM_USED = OFF_FREQ + 64 * 4;
 constexpr int SMEM_BYTES = SMEM_USED + 1024;                     // + slack to align the base to 1024
 static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
 
-// status words in the workspace
-enum { ST_CODE = 0, ST_ROLE = 1, ST_TILE = 2, ST_CHUNK = 3, ST_EXTRA = 4 };
 
 constexpr int MAX_LAYERS = 8;   // layers of one cross-layer group served by a single launch
 
@@ -91,50 +86,6 @@ struct Args {
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ uint64_t global_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait (about one second of wall time).  Returns false when the limit is hit (and raises
-// the abort flag) or when another role has already raised it.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try(bar, parity)) return true;
-  const uint64_t t0 = global_ns();
-  for (uint32_t it = 0; it < MAX_POLLS; ++it) {
-    if (mbar_try(bar, parity)) return true;
-    if ((it & 31u) == 31u) {
-      if (*abort_flag) return false;
-      if (global_ns() - t0 > WAIT_LIMIT_NS) break;
-      __nanosleep(32);
-    }
-  }
-  *abort_flag = 1;
-  return false;
-}
 #ifdef XKV_TC_PROFILE
 // Debug build only: cycles spent in each kind of wait, summed over CTAs into status[8 + slot].
 #define XKV_PROF_WAIT_L(slot, leader, expr)                                          \
@@ -165,20 +116,6 @@ __device__ __forceinline__ bool epilogue_sync_aborted(volatile int* abort_flag) 
       : "r"(mine)
       : "memory");
   return any != 0;
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-      : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -225,41 +162,6 @@ __device__ __forceinline__ void sincos_reduced(float x, float& sn, float& cs) {
   r = fmaf(k, -3.019916050561733e-7f, r);
   sn = __sinf(r);
   cs = __cosf(r);
-}
-
-template <typename T> struct TypeTraits;
-template <> struct TypeTraits<__nv_bfloat16> {
-  static constexpr uint32_t kFmt = 1;
-  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
-  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
-  static __device__ __forceinline__ uint32_t ones2() { return 0x3F803F80u; }
-  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-};
-template <> struct TypeTraits<__half> {
-  static constexpr uint32_t kFmt = 0;
-  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
-  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
-  static __device__ __forceinline__ uint32_t ones2() { return 0x3C003C00u; }
-  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-};
-
-__device__ __forceinline__ void report(int* status, int code, int role, int tile, int chunk, int extra) {
-  if (atomicCAS(&status[ST_CODE], 0, code) == 0) {
-    status[ST_ROLE] = role;
-    status[ST_TILE] = tile;
-    status[ST_CHUNK] = chunk;
-    status[ST_EXTRA] = extra;
-  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -686,43 +588,6 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
   }
 }
 
-__global__ void clear_status_kernel(int* status) {
-  if (threadIdx.x < 64) status[threadIdx.x] = 0;
-}
-
-// ---------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (tried) return fn;
-  tried = true;
-  void* p = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-      q == cudaDriverEntryPointSuccess)
-    fn = reinterpret_cast<EncodeTiledFn>(p);
-  else
-    cudaGetLastError();
-  return fn;
-}
-
-bool encode(CUtensorMap* m, int dtype, int rank, const void* ptr, const cuuint64_t* dims, const cuuint64_t* strides,
-            const cuuint32_t* box) {
-  EncodeTiledFn fn = get_encode();
-  if (!fn) return false;
-  cuuint32_t es[5] = {1, 1, 1, 1, 1};
-  const CUtensorMapDataType dt = dtype == XKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  return fn(m, dt, (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-bool stride_ok(int64_t elems) { return elems > 0 && (elems * 2) % 16 == 0; }
-
 template <typename T, int G, bool LO>
 int launch(const TensorMaps& maps, const Args& args, cudaStream_t st) {
   auto kern = recon_tc_kernel<T, G, LO>;
@@ -813,7 +678,7 @@ static bool encode_b(CUtensorMap* m, const xkv_decode_params& p, int b_batched) 
   const int64_t sb = b_batched ? p.kp_sb : (int64_t)KVH * p.k_rank * D * 4;
   const cuuint64_t strides[3] = {(cuuint64_t)p.kp_sr * 2, (cuuint64_t)p.kp_sh * 2, (cuuint64_t)sb * 2};
   const cuuint32_t box[4] = {64, BK, 1, 1};
-  return encode(m, p.dtype, 4, p.k_proj, dims, strides, box);
+  return encode_tiled_16bit(m, p.dtype, 4, p.k_proj, dims, strides, box);
 }
 
 static bool encode_v(CUtensorMap* m, const xkv_decode_params& p) {
@@ -821,7 +686,7 @@ static bool encode_v(CUtensorMap* m, const xkv_decode_params& p) {
   const int64_t sb = p.batch > 1 ? p.v_sb : (int64_t)p.kv_len * KVH * D * 4;
   const cuuint64_t strides[3] = {(cuuint64_t)p.v_sh * 2, (cuuint64_t)p.v_sl * 2, (cuuint64_t)sb * 2};
   const cuuint32_t box[4] = {64, 1, TILE_M, 1};
-  return encode(m, p.dtype, 4, p.v, dims, strides, box);
+  return encode_tiled_16bit(m, p.dtype, 4, p.v, dims, strides, box);
 }
 
 int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcPlan& pl, void* ws,
@@ -838,7 +703,7 @@ int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcP
     const int64_t sb = p.batch > 1 ? p.k_sb : (int64_t)p.kv_len * p.k_sl;
     const cuuint64_t strides[2] = {(cuuint64_t)p.k_sl * 2, (cuuint64_t)sb * 2};
     const cuuint32_t box[3] = {BK, TILE_M, 1};
-    if (!encode(&maps.a, p.dtype, 3, p.k, dims, strides, box)) return XKV_ERR_NO_DEVICE;
+    if (!encode_tiled_16bit(&maps.a, p.dtype, 3, p.k, dims, strides, box)) return XKV_ERR_NO_DEVICE;
   }
   const int b_batched = (p.kp_sb != 0 && p.batch > 1) ? 1 : 0;
   for (int i = 0; i < MAX_LAYERS; ++i) {

@@ -53,4 +53,13 @@ bool recon_tc_group_plan(const xkv_decode_params* layers, int n, ReconTcPlan* pl
 int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcPlan& plan, void* ws,
                           cudaStream_t st);
 
+// ---- dense GQA decode on mma.sync + TMA (dense_tc_sm100.cu) ----------------------------------
+struct DenseTcPlan {
+  int num_splits, tiles;
+  size_t off_partial, off_lse, total_bytes;
+};
+bool dense_tc_supported(const xkv_decode_params& p);
+bool dense_tc_plan(const xkv_decode_params& p, DenseTcPlan* plan);
+int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& plan, void* ws, cudaStream_t st);
+
 }  // namespace xkv
