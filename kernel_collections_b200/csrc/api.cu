@@ -50,12 +50,13 @@ int validate(const xkv_decode_params* p) {
   return XKV_OK;
 }
 
-enum class Path { kNone, kGeneric, kReconTc, kDenseTc };
+enum class Path { kNone, kGeneric, kReconTc, kDenseTc, kLatentTc };
 
 struct Plans {
   GenericPlan generic;
   ReconTcPlan recon;
   DenseTcPlan dense;
+  LatentTcPlan latent;
 };
 
 Path select(const xkv_decode_params& p, Plans* pl) {
@@ -63,6 +64,7 @@ Path select(const xkv_decode_params& p, Plans* pl) {
   if (!(p.flags & XKV_FLAG_FORCE_GENERIC)) {
     if (recon_tc_supported(p) && recon_tc_plan(p, &pl->recon)) return Path::kReconTc;
     if (dense_tc_supported(p) && dense_tc_plan(p, &pl->dense)) return Path::kDenseTc;
+    if (latent_tc_supported(p) && latent_tc_plan(p, &pl->latent)) return Path::kLatentTc;
   }
   if (generic_plan(p, gp)) return Path::kGeneric;
   return Path::kNone;
@@ -106,6 +108,7 @@ const char* xkv_decode_plan(const xkv_decode_params* p) {
   switch (select(*p, &pl)) {
     case Path::kReconTc: return "recon_tc";
     case Path::kDenseTc: return "dense_tc";
+    case Path::kLatentTc: return "latent_tc";
     case Path::kGeneric: return "generic";
     default: return nullptr;
   }
@@ -117,6 +120,7 @@ size_t xkv_decode_workspace_bytes(const xkv_decode_params* p) {
   switch (select(*p, &pl)) {
     case Path::kReconTc: return pl.recon.total_bytes;
     case Path::kDenseTc: return pl.dense.total_bytes;
+    case Path::kLatentTc: return pl.latent.total_bytes;
     case Path::kGeneric: return pl.generic.total_bytes;
     default: return 0;
   }
@@ -134,6 +138,9 @@ int xkv_decode(const xkv_decode_params* p, void* ws, size_t ws_bytes, void* stre
     case Path::kDenseTc:
       if (!ws || ws_bytes < pl.dense.total_bytes) return XKV_ERR_WORKSPACE;
       return dense_tc_decode(*p, pl.dense, ws, st);
+    case Path::kLatentTc:
+      if (!ws || ws_bytes < pl.latent.total_bytes) return XKV_ERR_WORKSPACE;
+      return latent_tc_decode(*p, pl.latent, ws, st);
     case Path::kGeneric:
       if (!ws || ws_bytes < pl.generic.total_bytes) return XKV_ERR_WORKSPACE;
       return generic_decode(*p, pl.generic, ws, st);

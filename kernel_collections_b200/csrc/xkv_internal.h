@@ -62,4 +62,14 @@ bool dense_tc_supported(const xkv_decode_params& p);
 bool dense_tc_plan(const xkv_decode_params& p, DenseTcPlan* plan);
 int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& plan, void* ws, cudaStream_t st);
 
+// ---- shared-latent decode (absorbed factorized K / V, MLA) on mma.sync + TMA (latent_tc_sm100.cu)
+struct LatentTcPlan {
+  int heads_per_cta, stages, num_splits, tiles;
+  size_t smem_bytes;
+  size_t off_qeff, off_partial, off_lse, total_bytes;
+};
+bool latent_tc_supported(const xkv_decode_params& p);
+bool latent_tc_plan(const xkv_decode_params& p, LatentTcPlan* plan);
+int latent_tc_decode(const xkv_decode_params& p, const LatentTcPlan& plan, void* ws, cudaStream_t st);
+
 }  // namespace xkv

@@ -1,0 +1,90 @@
+"""GPU parity of the shared-latent decode kernel (absorbed factorized K / V and MLA; bf16 / fp16,
+ranks in multiples of 64 / 128): against the CPU oracle and the portable kernel."""
+import pytest
+import torch
+
+import kernel_collections_b200 as K
+from kernel_collections_b200 import flash_recontruction as FR
+from kernel_collections_b200 import flash_decoding as FD
+from kernel_collections_b200 import _C, ops
+from oracle import xkv_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def close(got, want, what, ta=2e-2, tr=1e-2):
+    assert torch.isfinite(got.float()).all(), what
+    ma, rel = O.error_metrics(got, want)
+    assert ma <= ta * max(1.0, want.abs().max().item()) and rel <= tr, f"{what}: max_abs={ma:.3e} rel_l2={rel:.3e}"
+
+
+def status_ok():
+    rc, detail = _C.last_status(torch.device(DEV))
+    assert rc == 0, detail
+
+
+FACT = [  # b, H, KVH, D, L, Rk, Rv
+    (2, 32, 8, 128, 1000, 256, 384), (1, 32, 8, 128, 33, 64, 128), (3, 16, 4, 64, 257, 128, 128),
+    (1, 64, 8, 128, 2048, 512, 512), (2, 8, 2, 128, 700, 768, 512), (1, 40, 8, 128, 31, 192, 256),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", FACT)
+def test_factorized_absorbed(dtype, case):
+    b, H, KVH, D, L, Rk, Rv = case
+    g = torch.Generator().manual_seed(41)
+    q = torch.randn(b, H, 1, D, generator=g).to(dtype)
+    Ak = torch.randn(b, L, Rk, generator=g).to(dtype)
+    Bk = (torch.randn(b, KVH, Rk, D, generator=g) / Rk ** 0.5).to(dtype)
+    Av = torch.randn(b, L, Rv, generator=g).to(dtype)
+    Bv = (torch.randn(b, KVH, Rv, D, generator=g) / Rv ** 0.5).to(dtype)
+    qd, Akd, Bkd, Avd, Bvd = (x.to(DEV) for x in (q, Ak, Bk, Av, Bv))
+    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT, q=qd[:, :, 0], k=Akd, k_proj=Bkd, v=Avd,
+              v_proj=Bvd, sm_scale=D ** -0.5)
+    assert ops.plan(**kw) == "latent_tc"
+    got = K.group_query_attention_factorized(qd, Akd, Bkd, Avd, Bvd)
+    status_ok()
+    close(got, O.gqa_factorized(q, Ak, Bk, Av, Bv), "factorized (latent_tc) vs oracle")
+    gen = ops.decode(entry="xkv_absorbed_decode", force_generic=True, **kw)
+    close(got[:, :, 0], gen.float().cpu(), "latent_tc vs portable kernel", 1e-2, 6e-3)
+    assert torch.equal(got, K.group_query_attention_factorized(qd, Akd, Bkd, Avd, Bvd))
+    # fused xKV entry point with its own scale and in-place output
+    o = torch.zeros(b, H, D, dtype=dtype, device=DEV)
+    FR.gqa_xKV_no_pe(qd[:, :, 0], Akd, Bkd, Avd, Bvd, o, torch.full((b,), 8, dtype=torch.int32, device=DEV), 8, 0.07)
+    close(o, O.xkv_fused(q[:, :, 0], Ak, Bk, Av, Bv, 0.07), "gqa_xKV_no_pe (latent_tc)")
+
+
+MLA = [  # b, H, lora, rope, L
+    (2, 16, 128, 64, 203), (1, 128, 512, 64, 1500), (3, 64, 256, 64, 64), (1, 32, 512, 64, 4097),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", MLA)
+def test_mla(dtype, case):
+    b, H, lora, rope, L = case
+    g = torch.Generator().manual_seed(42)
+    qn = (torch.randn(b, H, lora, generator=g) / 3).to(dtype)
+    qr = (torch.randn(b, H, rope, generator=g) / 3).to(dtype)
+    c = (torch.randn(b, L, 1, lora, generator=g) / 3).to(dtype)
+    kr = (torch.randn(b, L, 1, rope, generator=g) / 3).to(dtype)
+    qnd, qrd, cd, krd = (x.to(DEV) for x in (qn, qr, c, kr))
+    got = FD.mla2.mla_decode_attention_fwd(qnd, qrd, cd, krd, 0.3)
+    status_ok()
+    close(got, O.mla_decode(qn, qr, c, kr, 0.3), "mla2 fwd (latent_tc)")
+    # absorbed form with W_uk / W_uv
+    nope, vd = 128, 128
+    qq = torch.randn(b, H, nope, generator=g).to(dtype)
+    Wk = (torch.randn(H, nope, lora, generator=g) / lora ** 0.5).to(dtype)
+    Wv = (torch.randn(H, lora, vd, generator=g) / lora ** 0.5).to(dtype)
+    sc = (nope + rope) ** -0.5
+    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT, q=qq.to(DEV), k=cd[:, :, 0], v=cd[:, :, 0],
+              k_proj=Wk.to(DEV).permute(0, 2, 1).unsqueeze(0), v_proj=Wv.to(DEV).unsqueeze(0), q_tail=qrd,
+              k_tail=krd[:, :, 0], sm_scale=sc, num_kv_heads=1)
+    assert ops.plan(**kw) == "latent_tc"
+    got2 = K.mla_absorbed_decode(qq.to(DEV), qrd, cd[:, :, 0], krd[:, :, 0], Wk.to(DEV), Wv.to(DEV), sc)
+    status_ok()
+    close(got2, O.mla_absorbed(qq, qr, c[:, :, 0], kr[:, :, 0], Wk, Wv, sc), "mla_absorbed_decode (latent_tc)")
+    assert torch.equal(got2, K.mla_absorbed_decode(qq.to(DEV), qrd, cd[:, :, 0], krd[:, :, 0], Wk.to(DEV), Wv.to(DEV), sc))
