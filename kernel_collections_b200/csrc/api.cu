@@ -50,13 +50,14 @@ int validate(const xkv_decode_params* p) {
   return XKV_OK;
 }
 
-enum class Path { kNone, kGeneric, kReconTc, kDenseTc, kLatentTc };
+enum class Path { kNone, kGeneric, kReconTc, kDenseTc, kLatentTc, kTwoPass };
 
 struct Plans {
   GenericPlan generic;
   ReconTcPlan recon;
   DenseTcPlan dense;
   LatentTcPlan latent;
+  TwoPassPlan two_pass;
 };
 
 Path select(const xkv_decode_params& p, Plans* pl) {
@@ -65,6 +66,7 @@ Path select(const xkv_decode_params& p, Plans* pl) {
     if (recon_tc_supported(p) && recon_tc_plan(p, &pl->recon)) return Path::kReconTc;
     if (dense_tc_supported(p) && dense_tc_plan(p, &pl->dense)) return Path::kDenseTc;
     if (latent_tc_supported(p) && latent_tc_plan(p, &pl->latent)) return Path::kLatentTc;
+    if (two_pass_supported(&p, 1) && two_pass_plan(&p, 1, &pl->two_pass)) return Path::kTwoPass;
   }
   if (generic_plan(p, gp)) return Path::kGeneric;
   return Path::kNone;
@@ -109,6 +111,7 @@ const char* xkv_decode_plan(const xkv_decode_params* p) {
     case Path::kReconTc: return "recon_tc";
     case Path::kDenseTc: return "dense_tc";
     case Path::kLatentTc: return "latent_tc";
+    case Path::kTwoPass: return "two_pass";
     case Path::kGeneric: return "generic";
     default: return nullptr;
   }
@@ -121,6 +124,7 @@ size_t xkv_decode_workspace_bytes(const xkv_decode_params* p) {
     case Path::kReconTc: return pl.recon.total_bytes;
     case Path::kDenseTc: return pl.dense.total_bytes;
     case Path::kLatentTc: return pl.latent.total_bytes;
+    case Path::kTwoPass: return pl.two_pass.total_bytes;
     case Path::kGeneric: return pl.generic.total_bytes;
     default: return 0;
   }
@@ -141,6 +145,9 @@ int xkv_decode(const xkv_decode_params* p, void* ws, size_t ws_bytes, void* stre
     case Path::kLatentTc:
       if (!ws || ws_bytes < pl.latent.total_bytes) return XKV_ERR_WORKSPACE;
       return latent_tc_decode(*p, pl.latent, ws, st);
+    case Path::kTwoPass:
+      if (!ws || ws_bytes < pl.two_pass.total_bytes) return XKV_ERR_WORKSPACE;
+      return two_pass_decode(p, 1, pl.two_pass, ws, st);
     case Path::kGeneric:
       if (!ws || ws_bytes < pl.generic.total_bytes) return XKV_ERR_WORKSPACE;
       return generic_decode(*p, pl.generic, ws, st);
@@ -211,6 +218,8 @@ size_t xkv_group_decode_workspace_bytes(const xkv_decode_params* layers, int n) 
   if (group_check(layers, n) != XKV_OK) return 0;
   ReconTcPlan rp;
   if (recon_tc_group_supported(layers, n) && recon_tc_group_plan(layers, n, &rp)) return rp.total_bytes;
+  TwoPassPlan tp;
+  if (two_pass_supported(layers, n) && two_pass_plan(layers, n, &tp)) return tp.total_bytes;
   size_t mx = 0;
   for (int i = 0; i < n; ++i) {
     size_t b = xkv_decode_workspace_bytes(&layers[i]);
@@ -226,7 +235,12 @@ int xkv_group_decode(const xkv_decode_params* layers, int n, void* ws, size_t ws
   ReconTcPlan rp;
   if (recon_tc_group_supported(layers, n) && recon_tc_group_plan(layers, n, &rp)) {
     if (!ws || ws_bytes < rp.total_bytes) return XKV_ERR_WORKSPACE;
-    return recon_tc_group_decode(layers, n, rp, ws, static_cast<cudaStream_t>(stream));
+    return recon_tc_group_decode(layers, n, rp, ws, static_cast<cudaStream_t>(stream), nullptr);
+  }
+  TwoPassPlan tp;
+  if (two_pass_supported(layers, n) && two_pass_plan(layers, n, &tp)) {
+    if (!ws || ws_bytes < tp.total_bytes) return XKV_ERR_WORKSPACE;
+    return two_pass_decode(layers, n, tp, ws, static_cast<cudaStream_t>(stream));
   }
   for (int i = 0; i < n; ++i) {
     rc = xkv_decode(&layers[i], ws, ws_bytes, stream);

@@ -39,6 +39,9 @@ struct Args {
   float* partial_o;          // [batch][H][splits][128]
   float* lse;                // [batch][H][splits]
   int* status;
+  float* logits;             // logits-only mode: fp32 sm_scale * q.k at [b * lg_sb + h * lg_sh + token]
+  int64_t lg_sb, lg_sh;
+  float sm_scale;
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, __nv_bfloat16) {
@@ -56,7 +59,8 @@ __device__ __forceinline__ float2 unpack2(uint32_t u, __half) {
   return __half22float2(*reinterpret_cast<__half2*>(&u));
 }
 
-template <typename T>
+// LO: logits only (first pass of a two-pass decode): K is streamed, V is not, no softmax / P.V.
+template <typename T, bool LO>
 __global__ void __launch_bounds__(NTHREADS, 2)
 dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const Args a) {
   extern __shared__ uint8_t smem_raw[];
@@ -99,12 +103,14 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
           report(a.status, XKV_ERR_TIMEOUT, 0, tile, kvh, b);
           break;
         }
-        mbar_expect_tx(bar_full(stage), STAGE_BYTES);
+        mbar_expect_tx(bar_full(stage), LO ? KV_BYTES : STAGE_BYTES);
         const uint32_t sk = base + stage * STAGE_BYTES;
         tma_load_4d(sk, &tmK, 0, kvh, tile * TILE, b, bar_full(stage));
         tma_load_4d(sk + KV_BYTES / 2, &tmK, 64, kvh, tile * TILE, b, bar_full(stage));
-        tma_load_4d(sk + KV_BYTES, &tmV, 0, kvh, tile * TILE, b, bar_full(stage));
-        tma_load_4d(sk + KV_BYTES + KV_BYTES / 2, &tmV, 64, kvh, tile * TILE, b, bar_full(stage));
+        if (!LO) {
+          tma_load_4d(sk + KV_BYTES, &tmV, 0, kvh, tile * TILE, b, bar_full(stage));
+          tma_load_4d(sk + KV_BYTES + KV_BYTES / 2, &tmV, 64, kvh, tile * TILE, b, bar_full(stage));
+        }
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
@@ -156,8 +162,29 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
           TypeTraits<T>::mma(sc[1], qf[ks], kb[2], kb[3]);
         }
       }
-      // ---- online softmax, rows g (c0,c1) and g+8 (c2,c3) -------------------------------------------
       const int tok0 = tile * TILE + cw * 16 + 2 * t;
+      if (LO) {
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+          const int row = g + rr * 8;
+          if (row < G) {
+            float* lg = a.logits + (int64_t)b * a.lg_sb + (int64_t)(kvh * G + row) * a.lg_sh;
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int tok = tok0 + n * 8 + e;
+                if (tok < a.kv_len) lg[tok] = sc[n][rr * 2 + e] * a.sm_scale;
+              }
+          }
+        }
+        __syncwarp();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (lane == 0) mbar_arrive(bar_empty(stage));
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        continue;
+      }
+      // ---- online softmax, rows g (c0,c1) and g+8 (c2,c3) -------------------------------------------
       float p[2][4];
       float alpha[2];
 #pragma unroll
@@ -227,6 +254,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     return;
   }
+  if (LO) return;
   float* scratch = reinterpret_cast<float*>(sm);            // [warp][row 16][D + 2]
   if (warp >= 1) {
     const int cw = warp - 1;
@@ -267,9 +295,9 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   }
 }
 
-template <typename T>
+template <typename T, bool LO>
 int launch(const CUtensorMap& tK, const CUtensorMap& tV, const Args& a, cudaStream_t st) {
-  auto kern = dense_tc_kernel<T>;
+  auto kern = dense_tc_kernel<T, LO>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
     cudaGetLastError();
     return XKV_ERR_LAUNCH;
@@ -288,19 +316,28 @@ bool encode_kv(CUtensorMap* m, int dtype, const void* ptr, int kvh, int L, int b
 
 }  // namespace
 
-bool dense_tc_supported(const xkv_decode_params& p) {
-  if (p.score_mode != XKV_SCORE_DENSE || p.value_mode != XKV_VALUE_DENSE) return false;
-  if (p.flags & XKV_FLAG_LOGITS_ONLY) return false;
+static bool keys_ok(const xkv_decode_params& p) {
+  if (p.score_mode != XKV_SCORE_DENSE) return false;
   if (p.dtype != XKV_BF16 && p.dtype != XKV_F16) return false;
-  if (p.head_dim != D || p.value_dim != D || p.tail_dim != 0 || p.logit_cap > 0.f) return false;
-  const int G = p.num_heads / p.num_kv_heads;
-  if (G > 16) return false;
-  if (!aligned16(p.k) || !aligned16(p.v) || (reinterpret_cast<uintptr_t>(p.q) & 3u)) return false;
-  if (!stride_ok(p.k_sl) || !stride_ok(p.v_sl)) return false;
-  if (p.num_kv_heads > 1 && (!stride_ok(p.k_sh) || !stride_ok(p.v_sh))) return false;
-  if (p.batch > 1 && (!stride_ok(p.k_sb) || !stride_ok(p.v_sb))) return false;
+  if (p.head_dim != D || p.tail_dim != 0 || p.logit_cap > 0.f) return false;
+  if (p.num_heads / p.num_kv_heads > 16) return false;
+  if (!aligned16(p.k) || (reinterpret_cast<uintptr_t>(p.q) & 3u)) return false;
+  if (!stride_ok(p.k_sl) || (p.num_kv_heads > 1 && !stride_ok(p.k_sh)) || (p.batch > 1 && !stride_ok(p.k_sb))) return false;
   if (p.q_sh % 2 != 0 || p.q_sb % 2 != 0) return false;
   return true;
+}
+
+bool dense_tc_supported(const xkv_decode_params& p) {
+  if (!keys_ok(p) || p.value_mode != XKV_VALUE_DENSE || (p.flags & XKV_FLAG_LOGITS_ONLY)) return false;
+  if (p.value_dim != D || !aligned16(p.v) || !stride_ok(p.v_sl)) return false;
+  if (p.num_kv_heads > 1 && !stride_ok(p.v_sh)) return false;
+  if (p.batch > 1 && !stride_ok(p.v_sb)) return false;
+  return true;
+}
+
+// First pass of the two-pass decode: fp32 logits of dense keys.
+bool dense_tc_logits_supported(const xkv_decode_params& p) {
+  return keys_ok(p) && !(p.flags & XKV_FLAG_FORCE_GENERIC);
 }
 
 bool dense_tc_plan(const xkv_decode_params& p, DenseTcPlan* pl) {
@@ -326,11 +363,16 @@ bool dense_tc_plan(const xkv_decode_params& p, DenseTcPlan* pl) {
   return true;
 }
 
-int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& pl, void* ws, cudaStream_t st) {
+int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& pl, void* ws, cudaStream_t st,
+                    const LogitsSink* sink) {
   char* w = static_cast<char*>(ws);
   CUtensorMap tK, tV;
   if (!encode_kv(&tK, p.dtype, p.k, p.num_kv_heads, p.kv_len, p.batch, p.k_sh, p.k_sl, p.k_sb)) return XKV_ERR_NO_DEVICE;
-  if (!encode_kv(&tV, p.dtype, p.v, p.num_kv_heads, p.kv_len, p.batch, p.v_sh, p.v_sl, p.v_sb)) return XKV_ERR_NO_DEVICE;
+  if (sink) {
+    tV = tK;
+  } else if (!encode_kv(&tV, p.dtype, p.v, p.num_kv_heads, p.kv_len, p.batch, p.v_sh, p.v_sl, p.v_sb)) {
+    return XKV_ERR_NO_DEVICE;
+  }
   int* status = reinterpret_cast<int*>(w);
   clear_status_kernel<<<1, 64, 0, st>>>(status);
   Args a;
@@ -342,7 +384,12 @@ int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& pl, void* ws,
   a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
   a.lse = reinterpret_cast<float*>(w + pl.off_lse);
   a.status = status;
-  const int rc = p.dtype == XKV_BF16 ? launch<__nv_bfloat16>(tK, tV, a, st) : launch<__half>(tK, tV, a, st);
+  a.logits = nullptr; a.lg_sb = a.lg_sh = 0; a.sm_scale = p.sm_scale;
+  if (sink) {
+    a.logits = sink->ptr; a.lg_sb = sink->sb; a.lg_sh = sink->sh;
+    return p.dtype == XKV_BF16 ? launch<__nv_bfloat16, true>(tK, tV, a, st) : launch<__half, true>(tK, tV, a, st);
+  }
+  const int rc = p.dtype == XKV_BF16 ? launch<__nv_bfloat16, false>(tK, tV, a, st) : launch<__half, false>(tK, tV, a, st);
   if (rc != XKV_OK) return rc;
   return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, D, D, nullptr, 1, 0, 0,
                       0, 0, p.o_sb, p.o_sh, st);

@@ -293,7 +293,7 @@ decode_partial_kernel(const xkv_decode_params p, const PartialGeom g, const floa
 template <typename T>
 __global__ void __launch_bounds__(NT)
 merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ lse, T* __restrict__ out,
-             int num_heads, int S, int Dacc, int Dv, const T* __restrict__ v_proj, int v_div,
+             int num_heads, int heads_total, int head_offset, int S, int Dacc, int Dv, const T* __restrict__ v_proj, int v_div,
              int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd, int64_t o_sb, int64_t o_sh) {
   extern __shared__ float smem[];
   float* w_s = smem;          // [S]
@@ -302,8 +302,11 @@ merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ lse,
   __shared__ float bcast[2];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int h = blockIdx.x, b = blockIdx.y;
-  const float* ls = lse + ((int64_t)b * num_heads + h) * S;
-  const float* po = partial_o + ((int64_t)b * num_heads + h) * S * (int64_t)Dacc;
+  // the partials may belong to a wider buffer of stacked heads (several layers side by side)
+  const int64_t prow = (int64_t)b * heads_total + head_offset + h;
+  const float* ls = lse + prow * S;
+  const float* po = partial_o + prow * S * (int64_t)Dacc;
+  (void)num_heads;
 
   float mx = -CUDART_INF_F;
   for (int s = tid; s < S; s += NT) mx = fmaxf(mx, ls[s]);
@@ -491,13 +494,15 @@ int generic_decode_builtin_scratch(const xkv_decode_params& p, const GenericPlan
 int launch_merge(const float* partial_o, const float* lse, void* out, int dtype, int batch, int num_heads,
                  int num_splits, int acc_dim, int value_dim, const void* v_proj, int v_proj_heads,
                  int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd, int64_t o_sb, int64_t o_sh,
-                 cudaStream_t st) {
+                 cudaStream_t st, int heads_total, int head_offset) {
+  if (heads_total <= 0) heads_total = num_heads;
   const size_t smem = (size_t)(num_splits + acc_dim) * sizeof(float);
   if (smem > 40 * 1024) return XKV_ERR_UNSUPPORTED;
   const dim3 grid(num_heads, batch);
   const int div = v_proj ? num_heads / v_proj_heads : 1;
 #define XKV_MERGE(T)                                                                                  \
-  merge_kernel<T><<<grid, NT, smem, st>>>(partial_o, lse, static_cast<T*>(out), num_heads, num_splits, \
+  merge_kernel<T><<<grid, NT, smem, st>>>(partial_o, lse, static_cast<T*>(out), num_heads, heads_total, \
+                                          head_offset, num_splits,                                  \
                                           acc_dim, value_dim, static_cast<const T*>(v_proj), div, vp_sb, \
                                           vp_sh, vp_sr, vp_sd, o_sb, o_sh)
   switch (dtype) {

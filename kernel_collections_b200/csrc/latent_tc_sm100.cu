@@ -29,6 +29,8 @@ struct Args {
   int num_splits, tiles_per_row, stages;
   float scale_log2;
   const void* qeff;                     // [batch][H][dk], working dtype
+  const float* logits;                  // FL mode: fp32 logits [b * lg_sb + h * lg_sh + token] from a first pass
+  int64_t lg_sb, lg_sh;
   float* partial_o;                     // [batch][H][splits][rv]
   float* lse;                           // [batch][H][splits]
   int* status;
@@ -78,7 +80,9 @@ __device__ __forceinline__ bool group_bar_aborted(volatile int* abort_flag) {
 }
 
 // HB: heads per CTA (32 or 64).  NT: 8-column value n-tiles per warp (rv <= 64 * NT).
-template <typename T, int HB, int NT>
+// FL: the scores come as fp32 logits from a first pass (reconstructed or dense keys) instead of
+//     Q_eff . K^T; only the value latent is streamed.
+template <typename T, int HB, int NT, bool FL>
 __global__ void __launch_bounds__(NTHREADS, 1)
 latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmKt,
                  const __grid_constant__ CUtensorMap tmV, const Args a) {
@@ -95,7 +99,7 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   const int h0 = hblk * HB;
   const int tile_begin = (int)(((int64_t)split * a.tiles_per_row) / a.num_splits);
   const int tile_end = (int)(((int64_t)(split + 1) * a.tiles_per_row) / a.num_splits);
-  const int KB = a.dk / 64, KBK = a.rk / 64, VB = a.rv / 64;
+  const int KB = FL ? 0 : a.dk / 64, KBK = FL ? 0 : a.rk / 64, VB = a.rv / 64;
   const int vblk0 = a.alias_v ? 0 : KB;             // first 64-column block of the value rows in a stage
   const int stage_blocks = a.alias_v ? KB : KB + VB;
   const uint32_t BLK = TILE * 128;                  // bytes of one [32 x 64] block
@@ -120,7 +124,7 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   // resident queries: row r, block kb -> swizzled [HB x 128 B] block; rows past num_heads are zero
-  {
+  if (!FL) {
     const T* qg = static_cast<const T*>(a.qeff) + ((int64_t)b * a.num_heads + h0) * a.dk;
     const int chunks = HB * KB * 8;                 // 16-byte chunks
     for (int c = threadIdx.x; c < chunks; c += NTHREADS) {
@@ -171,6 +175,24 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     uint32_t phase = 0;
     const int mi = lane >> 3, r8 = lane & 7;
     const int nvt = a.rv / 64;                      // value n-tiles this warp really owns (<= NT)
+    // FL: logits of this warp's units, fetched one tile ahead (rows g / g+8, tokens 2t / 2t+1)
+    float lgn[UPW][4];
+    auto fetch_logits = [&](int tile) {
+#pragma unroll
+      for (int u = 0; u < UPW; ++u) {
+        const int j = cw / MT + u * (NCW / MT);
+        const int tok = tile * TILE + j * 8 + 2 * t;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int h = h0 + mt_w * 16 + g + (i >> 1) * 8;
+          const int tk = tok + (i & 1);
+          lgn[u][i] = (tile < tile_end && h < a.num_heads && tk < a.kv_len)
+                          ? __ldg(a.logits + (int64_t)b * a.lg_sb + (int64_t)h * a.lg_sh + tk)
+                          : 0.f;
+        }
+      }
+    };
+    if (FL) fetch_logits(tile_begin);
     for (int tile = tile_begin; tile < tile_end; ++tile) {
       bool ok = mbar_wait(bar_full(stage), phase, abort_flag);
       if (!__all_sync(0xffffffffu, ok) && lane == 0) report(a.status, XKV_ERR_TIMEOUT, 1, tile, hblk, b);
@@ -180,6 +202,13 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       float sc[UPW][4];
 #pragma unroll
       for (int u = 0; u < UPW; ++u) { sc[u][0] = sc[u][1] = sc[u][2] = sc[u][3] = 0.f; }
+      if (FL) {
+#pragma unroll
+        for (int u = 0; u < UPW; ++u)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sc[u][i] = lgn[u][i];
+        fetch_logits(tile + 1);
+      }
       for (int kb = 0; kb < KB; ++kb) {
         const uint32_t qb = base + off_q + kb * (HB * 128);
         const uint32_t kblk = ss + kb * BLK;
@@ -382,10 +411,10 @@ size_t smem_need(const xkv_decode_params& p, int hb, int stages) {
   return q + stages * stage + hb * 64 + hb * 16 + hb * 4 + 64 + 16;
 }
 
-template <typename T, int HB, int NT>
+template <typename T, int HB, int NT, bool FL>
 int launch(const CUtensorMap& tK, const CUtensorMap& tKt, const CUtensorMap& tV, const Args& a, int hblocks,
            size_t smem, cudaStream_t st) {
-  auto kern = latent_tc_kernel<T, HB, NT>;
+  auto kern = latent_tc_kernel<T, HB, NT, FL>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     cudaGetLastError();
     return XKV_ERR_LAUNCH;
@@ -394,16 +423,16 @@ int launch(const CUtensorMap& tK, const CUtensorMap& tKt, const CUtensorMap& tV,
   return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
 }
 
-template <typename T>
+template <typename T, bool FL>
 int dispatch(int hb, int nt, const CUtensorMap& tK, const CUtensorMap& tKt, const CUtensorMap& tV, const Args& a,
              int hblocks, size_t smem, cudaStream_t st) {
   if (hb == 64) {
-    if (nt <= 4) return launch<T, 64, 4>(tK, tKt, tV, a, hblocks, smem, st);
-    return launch<T, 64, 8>(tK, tKt, tV, a, hblocks, smem, st);
+    if (nt <= 4) return launch<T, 64, 4, FL>(tK, tKt, tV, a, hblocks, smem, st);
+    return launch<T, 64, 8, FL>(tK, tKt, tV, a, hblocks, smem, st);
   }
-  if (nt <= 4) return launch<T, 32, 4>(tK, tKt, tV, a, hblocks, smem, st);
-  if (nt <= 8) return launch<T, 32, 8>(tK, tKt, tV, a, hblocks, smem, st);
-  return launch<T, 32, 16>(tK, tKt, tV, a, hblocks, smem, st);
+  if (nt <= 4) return launch<T, 32, 4, FL>(tK, tKt, tV, a, hblocks, smem, st);
+  if (nt <= 8) return launch<T, 32, 8, FL>(tK, tKt, tV, a, hblocks, smem, st);
+  return launch<T, 32, 16, FL>(tK, tKt, tV, a, hblocks, smem, st);
 }
 
 }  // namespace
@@ -490,12 +519,80 @@ int latent_tc_decode(const xkv_decode_params& p, const LatentTcPlan& pl, void* w
   a.status = status;
   const int hblocks = ceil_div(p.num_heads, pl.heads_per_cta);
   const int nt = p.v_rank / 64;
+  a.logits = nullptr; a.lg_sb = a.lg_sh = 0;
   const int rc = p.dtype == XKV_BF16
-                     ? dispatch<__nv_bfloat16>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st)
-                     : dispatch<__half>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st);
+                     ? dispatch<__nv_bfloat16, false>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st)
+                     : dispatch<__half, false>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st);
   if (rc != XKV_OK) return rc;
   return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, p.v_rank, p.value_dim,
                       p.v_proj, p.v_proj ? p.v_proj_heads : 1, p.vp_sb, p.vp_sh, p.vp_sr, p.vp_sd, p.o_sb, p.o_sh, st);
+}
+
+// ---- second pass of the two-pass decode: softmax(logits) . A_v over `heads` stacked heads ----------
+// The logits [batch][heads][kv_len] (fp32, already multiplied by sm_scale) come from a first pass
+// over reconstructed or dense keys; the value latent (batch, kv_len, v_rank) is streamed once for
+// all stacked heads of a head block.  Writes normalised partials + log-sum-exp like the one-pass
+// kernel; the caller merges (per layer) and applies the value projections.
+bool latent_pv_supported(const xkv_decode_params& p) {
+  if (p.value_mode != XKV_VALUE_LATENT || (p.flags & XKV_FLAG_LOGITS_ONLY)) return false;
+  if (p.dtype != XKV_BF16 && p.dtype != XKV_F16) return false;
+  if (p.v_rank % 128 != 0 || p.v_rank > 1024 || p.logit_cap > 0.f || p.tail_dim != 0) return false;
+  if (!aligned16(p.v) || !stride_ok(p.v_sl) || (p.batch > 1 && !stride_ok(p.v_sb))) return false;
+  return true;
+}
+
+bool latent_pv_plan(const xkv_decode_params& p, int heads, LatentTcPlan* pl) {
+  const int hb = (heads > 32 && p.v_rank <= 512) ? 64 : 32;
+  const size_t stage = (size_t)(p.v_rank / 64) * TILE * 128;
+  auto need = [&](int stages) { return stages * stage + hb * 64 + hb * 16 + hb * 4 + 64 + 16; };
+  int stages = 4;
+  while (stages > 2 && need(stages) > (size_t)MAX_SMEM) --stages;
+  pl->heads_per_cta = hb;
+  pl->stages = stages;
+  pl->smem_bytes = need(stages) + 1024;
+  const int tiles = ceil_div(p.kv_len, TILE);
+  const int rows = p.batch * ceil_div(heads, hb);
+  const int sms = device_sm_count();
+  int best_s = 1;
+  int64_t best_cost = -1;
+  const int max_s = tiles < 64 ? tiles : 64;
+  for (int s = 1; s <= max_s; ++s) {
+    const int64_t waves = ceil_div(rows * s, sms);
+    const int64_t cost = waves * (ceil_div(tiles, s) + 4);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = s; }
+  }
+  pl->num_splits = best_s;
+  pl->tiles = tiles;
+  size_t off = 0;
+  pl->off_qeff = off;
+  pl->off_partial = off;
+  off += align_up((size_t)p.batch * heads * best_s * p.v_rank * sizeof(float), 256);
+  pl->off_lse = off;
+  off += align_up((size_t)p.batch * heads * best_s * sizeof(float), 256);
+  pl->total_bytes = off;
+  return true;
+}
+
+int latent_pv_run(const xkv_decode_params& p, int heads, const LatentTcPlan& pl, const float* logits, void* ws,
+                  int* status, cudaStream_t st) {
+  char* w = static_cast<char*>(ws);
+  CUtensorMap tV;
+  if (!encode_rows(&tV, p.dtype, p.v, p.v_rank, p.kv_len, p.batch, p.v_sl, p.v_sb)) return XKV_ERR_NO_DEVICE;
+  Args a;
+  a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = heads;
+  a.dk = 0; a.rk = 0; a.rv = p.v_rank; a.alias_v = 0;
+  a.num_splits = pl.num_splits; a.tiles_per_row = pl.tiles; a.stages = pl.stages;
+  a.scale_log2 = 1.4426950408889634f;
+  a.qeff = nullptr;
+  a.logits = logits; a.lg_sb = (int64_t)heads * p.kv_len; a.lg_sh = p.kv_len;
+  a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
+  a.lse = reinterpret_cast<float*>(w + pl.off_lse);
+  a.status = status;
+  const int hblocks = ceil_div(heads, pl.heads_per_cta);
+  const int nt = p.v_rank / 64;
+  return p.dtype == XKV_BF16
+             ? dispatch<__nv_bfloat16, true>(pl.heads_per_cta, nt, tV, tV, tV, a, hblocks, pl.smem_bytes, st)
+             : dispatch<__half, true>(pl.heads_per_cta, nt, tV, tV, tV, a, hblocks, pl.smem_bytes, st);
 }
 
 }  // namespace xkv

@@ -79,7 +79,8 @@ struct Args {
   float* partial_o;      // [layer][batch][H][splits][128]
   float* lse;            // [layer][batch][H][splits]
   void* logits;
-  int64_t lg_sb, lg_sh;
+  int64_t lg_sb, lg_sh, lg_layer;   // logits[layer * lg_layer + b * lg_sb + h * lg_sh + token]
+  int logits_f32;                   // logits are fp32 (the first pass of a two-pass decode) instead of T
   int* status;
   int b_batched;
 };
@@ -408,9 +409,16 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
 
         if (LOGITS_ONLY) {
           if (valid) {
-            T* lg = static_cast<T*>(a.logits) + (int64_t)b * a.lg_sb + tok;
+            const int64_t off = (int64_t)layer * a.lg_layer + (int64_t)b * a.lg_sb + tok;
+            if (a.logits_f32) {
+              float* lg = static_cast<float*>(a.logits) + off;
 #pragma unroll
-            for (int i = 0; i < 2 * G; ++i) lg[(int64_t)(2 * c * G + i) * a.lg_sh] = TypeTraits<T>::from_f(s[i]);
+              for (int i = 0; i < 2 * G; ++i) lg[(int64_t)(2 * c * G + i) * a.lg_sh] = s[i];
+            } else {
+              T* lg = static_cast<T*>(a.logits) + off;
+#pragma unroll
+              for (int i = 0; i < 2 * G; ++i) lg[(int64_t)(2 * c * G + i) * a.lg_sh] = TypeTraits<T>::from_f(s[i]);
+            }
           }
         } else {
           // ---- online softmax over the tile, per head -------------------------------------------
@@ -690,11 +698,11 @@ static bool encode_v(CUtensorMap* m, const xkv_decode_params& p) {
 }
 
 int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcPlan& pl, void* ws,
-                          cudaStream_t st) {
+                          cudaStream_t st, const LogitsSink* sink) {
   const xkv_decode_params& p = layers[0];
   char* w = static_cast<char*>(ws);
   if (!aligned16(w)) return XKV_ERR_ALIGN;
-  const bool lo = (p.flags & XKV_FLAG_LOGITS_ONLY) != 0;
+  const bool lo = sink != nullptr || (p.flags & XKV_FLAG_LOGITS_ONLY) != 0;
   const int G = p.num_heads / p.num_kv_heads;
 
   TensorMaps maps;
@@ -734,7 +742,10 @@ int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcP
   a.inv_freq = p.inv_freq; a.theta = p.theta; a.pos_offset = p.pos_offset;
   a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
   a.lse = reinterpret_cast<float*>(w + pl.off_lse);
-  a.logits = p.logits; a.lg_sb = p.lg_sb; a.lg_sh = p.lg_sh;
+  a.logits = p.logits; a.lg_sb = p.lg_sb; a.lg_sh = p.lg_sh; a.lg_layer = 0; a.logits_f32 = 0;
+  if (sink) {
+    a.logits = sink->ptr; a.lg_sb = sink->sb; a.lg_sh = sink->sh; a.lg_layer = sink->layer; a.logits_f32 = 1;
+  }
   a.status = status;
   a.b_batched = b_batched;
 
@@ -758,7 +769,29 @@ int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcP
 }
 
 int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& pl, void* ws, cudaStream_t st) {
-  return recon_tc_group_decode(&p, 1, pl, ws, st);
+  return recon_tc_group_decode(&p, 1, pl, ws, st, nullptr);
+}
+
+// First pass of the two-pass decode: logits only, so the value side of the blocks is not looked at.
+bool recon_tc_logits_supported(const xkv_decode_params* layers, int n) {
+  if (n < 1 || n > MAX_LAYERS) return false;
+  for (int i = 0; i < n; ++i) {
+    xkv_decode_params t = layers[i];
+    t.flags |= XKV_FLAG_LOGITS_ONLY;
+    if (!recon_tc_supported(t) || (layers[i].flags & XKV_FLAG_FORCE_GENERIC)) return false;
+    const xkv_decode_params &a = layers[0], &b = layers[i];
+    if (a.q_sb != b.q_sb || a.q_sh != b.q_sh || a.sm_scale != b.sm_scale || a.theta != b.theta ||
+        a.pos_offset != b.pos_offset || a.inv_freq != b.inv_freq || a.k != b.k || a.k_sb != b.k_sb ||
+        a.k_sl != b.k_sl || (a.kp_sb != 0) != (b.kp_sb != 0))
+      return false;
+  }
+  return true;
+}
+
+bool recon_tc_logits_plan(const xkv_decode_params* layers, int n, ReconTcPlan* pl) {
+  xkv_decode_params t = layers[0];
+  t.flags |= XKV_FLAG_LOGITS_ONLY;
+  return plan_layers(t, n, pl);
 }
 
 }  // namespace xkv

@@ -34,7 +34,7 @@ int generic_decode_builtin_scratch(const xkv_decode_params& p, const GenericPlan
 int launch_merge(const float* partial_o, const float* lse, void* out, int dtype, int batch,
                  int num_heads, int num_splits, int acc_dim, int value_dim, const void* v_proj,
                  int v_proj_heads, int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd,
-                 int64_t o_sb, int64_t o_sh, cudaStream_t st);
+                 int64_t o_sb, int64_t o_sh, cudaStream_t st, int heads_total = 0, int head_offset = 0);
 int launch_rope_table(float* cos_sin, int kv_len, int half, int pos_offset, float theta,
                       const float* inv_freq, cudaStream_t st);
 
@@ -50,8 +50,15 @@ int recon_tc_decode(const xkv_decode_params& p, const ReconTcPlan& plan, void* w
 // one launch for the layers of a cross-layer group that share the key latent
 bool recon_tc_group_supported(const xkv_decode_params* layers, int n);
 bool recon_tc_group_plan(const xkv_decode_params* layers, int n, ReconTcPlan* plan);
+// fp32 logits of a first pass: logits[layer * layer + b * sb + h * sh + token]
+struct LogitsSink {
+  float* ptr;
+  int64_t sb, sh, layer;
+};
 int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcPlan& plan, void* ws,
-                          cudaStream_t st);
+                          cudaStream_t st, const LogitsSink* sink);
+bool recon_tc_logits_supported(const xkv_decode_params* layers, int n);
+bool recon_tc_logits_plan(const xkv_decode_params* layers, int n, ReconTcPlan* plan);
 
 // ---- dense GQA decode on mma.sync + TMA (dense_tc_sm100.cu) ----------------------------------
 struct DenseTcPlan {
@@ -60,7 +67,10 @@ struct DenseTcPlan {
 };
 bool dense_tc_supported(const xkv_decode_params& p);
 bool dense_tc_plan(const xkv_decode_params& p, DenseTcPlan* plan);
-int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& plan, void* ws, cudaStream_t st);
+struct LogitsSink;
+bool dense_tc_logits_supported(const xkv_decode_params& p);
+int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& plan, void* ws, cudaStream_t st,
+                    const LogitsSink* sink = nullptr);
 
 // ---- shared-latent decode (absorbed factorized K / V, MLA) on mma.sync + TMA (latent_tc_sm100.cu)
 struct LatentTcPlan {
@@ -71,5 +81,22 @@ struct LatentTcPlan {
 bool latent_tc_supported(const xkv_decode_params& p);
 bool latent_tc_plan(const xkv_decode_params& p, LatentTcPlan* plan);
 int latent_tc_decode(const xkv_decode_params& p, const LatentTcPlan& plan, void* ws, cudaStream_t st);
+// second pass of a two-pass decode: softmax over fp32 logits of `heads` stacked heads, times the value latent
+bool latent_pv_supported(const xkv_decode_params& p);
+bool latent_pv_plan(const xkv_decode_params& p, int heads, LatentTcPlan* plan);
+int latent_pv_run(const xkv_decode_params& p, int heads, const LatentTcPlan& plan, const float* logits, void* ws,
+                  int* status, cudaStream_t st);
+
+// ---- two-pass decode for factorized values behind dense / RoPE-reconstructed keys (two_pass.cu)
+struct TwoPassPlan {
+  int heads;                 // layers x heads, stacked for the second pass
+  ReconTcPlan recon;
+  DenseTcPlan dense;
+  LatentTcPlan pv;
+  size_t off_logits, off_pass1, off_pass2, total_bytes;
+};
+bool two_pass_supported(const xkv_decode_params* layers, int n);
+bool two_pass_plan(const xkv_decode_params* layers, int n, TwoPassPlan* plan);
+int two_pass_decode(const xkv_decode_params* layers, int n, const TwoPassPlan& plan, void* ws, cudaStream_t st);
 
 }  // namespace xkv

@@ -1,0 +1,94 @@
+"""GPU parity of the two-pass decode (tensor-core logits pass + shared-latent P.V pass): factorized
+values behind RoPE-reconstructed keys (single layer and cross-layer groups) and behind dense keys."""
+import pytest
+import torch
+
+import kernel_collections_b200 as K
+from kernel_collections_b200 import _C, ops
+from kernel_collections_b200.attention import as_key_proj
+from oracle import xkv_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+KVH, D = 8, 128
+
+
+def close(got, want, what, ta=2e-2, tr=1e-2):
+    assert torch.isfinite(got.float()).all(), what
+    ma, rel = O.error_metrics(got, want)
+    assert ma <= ta * max(1.0, want.abs().max().item()) and rel <= tr, f"{what}: max_abs={ma:.3e} rel_l2={rel:.3e}"
+
+
+def b4(B, b):
+    return B.view(B.shape[0], KVH, D).permute(1, 0, 2)[None].expand(b, -1, -1, -1)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", [(2, 4, 700, 128, 256), (1, 8, 1029, 256, 128), (3, 4, 31, 64, 1024)])
+def test_recon_rope_with_factorized_values(dtype, case):
+    b, G, L, R, Rv = case
+    theta = 500000.0
+    g = torch.Generator().manual_seed(51)
+    H = KVH * G
+    q = torch.randn(b, H, 1, D, generator=g).to(dtype)
+    A = torch.randn(b, L, R, generator=g).to(dtype)
+    B = (torch.randn(R, KVH * D, generator=g) / R ** 0.5).to(dtype)
+    Av = torch.randn(b, L, Rv, generator=g).to(dtype)
+    Bv = (torch.randn(Rv, KVH * D, generator=g) / Rv ** 0.5).to(dtype)
+    qd, Ad, Bd, Avd, Bvd = (x.to(DEV) for x in (q, A, B, Av, Bv))
+    kw = dict(score_mode=_C.SCORE_RECON_ROPE, value_mode=_C.VALUE_LATENT, q=qd[:, :, 0], k=Ad, k_proj=as_key_proj(Bd, D),
+              v=Avd, v_proj=as_key_proj(Bvd, D), sm_scale=D ** -0.5, theta=theta)
+    assert ops.plan(**kw) == "two_pass"
+    got = K.recon_rope_decode(qd, Ad, Bd, Avd, Bvd, theta=theta)
+    rc, detail = _C.last_status(torch.device(DEV))
+    assert rc == 0, detail
+    want = O.recon_rope_decode(q, A, b4(B, b), Av, theta, value_B=b4(Bv, b))
+    close(got, want, "two-pass vs oracle")
+    gen = K.recon_rope_decode(qd, Ad, Bd, Avd, Bvd, theta=theta, force_generic=True)
+    close(got, gen.float().cpu(), "two-pass vs portable kernel", 1e-2, 6e-3)
+    assert torch.equal(got, K.recon_rope_decode(qd, Ad, Bd, Avd, Bvd, theta=theta))
+    # the reference's own entry point for this mode (unscaled logits; q scaled down by the caller)
+    qs = (q * D ** -0.5).to(dtype)
+    Bb, Bvb = b4(B, b).contiguous(), b4(Bv, b).contiguous()
+    got2 = K.group_query_attention_factorized_RoPE(qs.to(DEV), Ad, Bb.to(DEV), Avd, Bvb.to(DEV), theta=theta)
+    close(got2, O.gqa_factorized_rope(qs, A, Bb, Av, Bvb, theta), "group_query_attention_factorized_RoPE")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16])
+@pytest.mark.parametrize("NL,b,L,R,Rv,G", [(4, 2, 600, 128, 256, 4), (2, 1, 1500, 64, 512, 8)])
+def test_group_with_shared_value_latent(dtype, NL, b, L, R, Rv, G):
+    theta = 500000.0
+    g = torch.Generator().manual_seed(52)
+    H = KVH * G
+    A = torch.randn(b, L, R, generator=g).to(dtype)
+    Av = torch.randn(b, L, Rv, generator=g).to(dtype)
+    qs = [torch.randn(b, H, 1, D, generator=g).to(dtype) for _ in range(NL)]
+    Bs = [(torch.randn(R, KVH * D, generator=g) / R ** 0.5).to(dtype) for _ in range(NL)]
+    Bvs = [(torch.randn(Rv, KVH * D, generator=g) / Rv ** 0.5).to(dtype) for _ in range(NL)]
+    got = K.xkv_group_decode([x.to(DEV) for x in qs], A.to(DEV), [x.to(DEV) for x in Bs], Av.to(DEV),
+                             [x.to(DEV) for x in Bvs], theta=theta)
+    rc, detail = _C.last_status(torch.device(DEV))
+    assert rc == 0, detail
+    want = O.group_decode(qs, A, [b4(x, b) for x in Bs], Av, [b4(x, b) for x in Bvs], theta)
+    for i in range(NL):
+        close(got[i], want[i], f"group layer {i}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", [(2, 32, 8, 900, 384), (1, 16, 2, 64, 128), (2, 8, 8, 2049, 512)])
+def test_dense_keys_with_factorized_values(dtype, case):
+    b, H, kvh, L, Rv = case
+    g = torch.Generator().manual_seed(53)
+    q = torch.randn(b, H, 1, D, generator=g).to(dtype)
+    k = torch.randn(b, kvh, L, D, generator=g).to(dtype)
+    Av = torch.randn(b, L, Rv, generator=g).to(dtype)
+    Bv = (torch.randn(b, kvh, Rv, D, generator=g) / Rv ** 0.5).to(dtype)
+    qd, kd, Avd, Bvd = (x.to(DEV) for x in (q, k, Av, Bv))
+    kw = dict(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_LATENT, q=qd[:, :, 0], k=kd.transpose(1, 2), v=Avd,
+              v_proj=Bvd, sm_scale=D ** -0.5)
+    assert ops.plan(**kw) == "two_pass"
+    got = K.group_query_attention_factorized_v_only(qd, kd, Avd, Bvd)
+    rc, detail = _C.last_status(torch.device(DEV))
+    assert rc == 0, detail
+    close(got, O.gqa_factorized_v_only(q, k, Av, Bv), "v_only two-pass vs oracle")
+    assert torch.equal(got, K.group_query_attention_factorized_v_only(qd, kd, Avd, Bvd))
