@@ -84,6 +84,33 @@ def w_group(reps):
                 flops=NL * (2 * b * L * R * KVH * D + 4 * b * H * L * D))
 
 
+def w_group_kv(reps):
+    """c3 as specified: 4 layers share the key latent AND the value latent (b32, L32768, R1024 each),
+    per-layer B_k / B_v.  Two passes: grouped tcgen05 logits, then one P.A_v pass over 128 stacked heads."""
+    NL, b, H, KVH, D, L, R = 4, 32, 32, 8, 128, 32768, 1024
+    Ak, Av = rnd(b, L, R), rnd(b, L, R)
+    qs = [rnd(b, H, 1, D) for _ in range(NL)]
+    Bs = [rnd(R, KVH * D, scale=R ** -0.5) for _ in range(NL)]
+    Bvs = [rnd(R, KVH * D, scale=R ** -0.5) for _ in range(NL)]
+    fn = lambda: A.xkv_group_decode(qs, Ak, Bs, Av, Bvs, theta=5e5)
+    return dict(workload="c3_group4_kv_factorized_b32_L32768_R1024", plan="two_pass (grouped)", tokens=b * NL,
+                ms=timed(fn, max(3, reps // 4)),
+                bytes=2 * (2 * b * L * R + NL * (2 * R * KVH * D + 2 * b * H * D)),
+                flops=NL * (2 * b * L * R * KVH * D + 2 * b * H * L * (D + R) + 2 * b * H * R * D))
+
+
+def w_v_only(reps):
+    """c3, V-only-factorized variant: per layer dense K (b32, L32768) + the shared value latent (R1024)."""
+    b, H, KVH, D, L, R = 32, 32, 8, 128, 32768, 1024
+    q, k, Av = rnd(b, H, 1, D), rnd(b, L, KVH, D), rnd(b, L, R)
+    Bv = rnd(b, KVH, R, D, scale=R ** -0.5)
+    fn = lambda: A.group_query_attention_factorized_v_only(q, k.transpose(1, 2), Av, Bv)
+    plan = ops.plan(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_LATENT, q=q[:, :, 0], k=k, v=Av, v_proj=Bv, sm_scale=1.0)
+    return dict(workload="c3_v_only_one_layer_b32_L32768_R1024", plan=plan, tokens=b, ms=timed(fn, max(3, reps // 4)),
+                bytes=2 * (b * L * (KVH * D + R) + b * KVH * R * D + 2 * b * H * D),
+                flops=2 * b * H * L * (D + R) + 2 * b * H * R * D)
+
+
 def w_factorized(reps):
     """Absorbed factorized K and V without RoPE (group_query_attention_factorized), c1 shape in bf16
     at a serving-sized batch."""
@@ -110,7 +137,8 @@ def w_mla(reps):
                 flops=b * L * H * (2 * (lora + rope) + 2 * lora) + 4 * b * H * nope * lora)
 
 
-WORKLOADS = {"dense": w_dense, "qab_logits": w_qab_logits, "group": w_group, "factorized": w_factorized, "mla": w_mla}
+WORKLOADS = {"dense": w_dense, "qab_logits": w_qab_logits, "group": w_group, "group_kv": w_group_kv,
+             "v_only": w_v_only, "factorized": w_factorized, "mla": w_mla}
 
 
 def main():
