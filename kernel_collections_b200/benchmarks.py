@@ -48,9 +48,16 @@ def rnd(*shape, dtype=torch.bfloat16, scale=1.0, dev="cuda"):
     return (torch.randn(*shape, device=dev) * scale).to(dtype)
 
 
+SMALL = False      # --small: quarter contexts, for profiler captures
+
+
+def ctx(L):
+    return L // 4 if SMALL else L
+
+
 def w_dense(reps):
     """Dense GQA decode at the c2 cache shape (group_query_attention / flash_decoding.gqa)."""
-    b, H, KVH, D, L = 16, 32, 8, 128, 16384
+    b, H, KVH, D, L = 16, 32, 8, 128, ctx(16384)
     q, k, v = rnd(b, H, 1, D), rnd(b, L, KVH, D), rnd(b, L, KVH, D)
     fn = lambda: A.group_query_attention(q, k.transpose(1, 2), v.transpose(1, 2))
     plan = ops.plan(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, q=q[:, :, 0], k=k, v=v, sm_scale=1.0)
@@ -114,7 +121,7 @@ def w_v_only(reps):
 def w_factorized(reps):
     """Absorbed factorized K and V without RoPE (group_query_attention_factorized), c1 shape in bf16
     at a serving-sized batch."""
-    b, H, KVH, D, L, R = 16, 32, 8, 128, 16384, 256
+    b, H, KVH, D, L, R = 16, 32, 8, 128, ctx(16384), 256
     q, Ak, Av = rnd(b, H, 1, D), rnd(b, L, R), rnd(b, L, R)
     Bk, Bv = rnd(b, KVH, R, D, scale=R ** -0.5), rnd(b, KVH, R, D, scale=R ** -0.5)
     fn = lambda: A.group_query_attention_factorized(q, Ak, Bk, Av, Bv)
@@ -126,7 +133,7 @@ def w_factorized(reps):
 
 def w_mla(reps):
     """c4: MLA absorbed decode, DeepSeek-V3 attention shape (b64, 128 heads, L8192)."""
-    b, H, lora, rope, nope, vd, L = 64, 128, 512, 64, 128, 128, 8192
+    b, H, lora, rope, nope, vd, L = 64, 128, 512, 64, 128, 128, ctx(8192)
     qn, qr = rnd(b, H, nope), rnd(b, H, rope)
     c, kr = rnd(b, L, lora), rnd(b, L, rope)
     Wk, Wv = rnd(H, nope, lora, scale=lora ** -0.5), rnd(H, lora, vd, scale=lora ** -0.5)
@@ -145,7 +152,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", nargs="*", default=list(WORKLOADS), choices=list(WORKLOADS))
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--small", action="store_true", help="quarter contexts (profiler-sized cases)")
     args = ap.parse_args()
+    global SMALL
+    SMALL = args.small
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
     hbm, tc, src = peaks()
