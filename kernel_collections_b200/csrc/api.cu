@@ -53,6 +53,7 @@ int validate(const xkv_decode_params* p) {
 enum class Path { kNone, kGeneric, kReconTc, kDenseTc, kLatentTc, kTwoPass };
 
 struct Plans {
+  xkv_decode_params rewritten;   // the call as the chosen kernel sees it (see as_latent)
   GenericPlan generic;
   ReconTcPlan recon;
   DenseTcPlan dense;
@@ -60,12 +61,34 @@ struct Plans {
   TwoPassPlan two_pass;
 };
 
+// A dense cache with ONE KV head (the packed MLA layout: keys [latent | rope], values a prefix of the
+// keys or a separate buffer) is a shared-latent call whose query is already in latent space.
+bool as_latent(const xkv_decode_params& p, xkv_decode_params* t) {
+  if (p.score_mode != XKV_SCORE_DENSE || p.value_mode != XKV_VALUE_DENSE || p.num_kv_heads != 1) return false;
+  if (p.flags & XKV_FLAG_LOGITS_ONLY) return false;
+  *t = p;
+  t->score_mode = XKV_SCORE_LATENT;
+  t->value_mode = XKV_VALUE_LATENT;
+  t->k_rank = p.head_dim;
+  t->k_proj = nullptr;
+  t->v_rank = p.value_dim;
+  t->v_proj = nullptr;
+  t->tail_dim = 0;
+  return true;
+}
+
 Path select(const xkv_decode_params& p, Plans* pl) {
   GenericPlan* gp = &pl->generic;
+  pl->rewritten = p;
   if (!(p.flags & XKV_FLAG_FORCE_GENERIC)) {
     if (recon_tc_supported(p) && recon_tc_plan(p, &pl->recon)) return Path::kReconTc;
     if (dense_tc_supported(p) && dense_tc_plan(p, &pl->dense)) return Path::kDenseTc;
     if (latent_tc_supported(p) && latent_tc_plan(p, &pl->latent)) return Path::kLatentTc;
+    xkv_decode_params t;
+    if (as_latent(p, &t) && latent_tc_supported(t) && latent_tc_plan(t, &pl->latent)) {
+      pl->rewritten = t;
+      return Path::kLatentTc;
+    }
     if (two_pass_supported(&p, 1) && two_pass_plan(&p, 1, &pl->two_pass)) return Path::kTwoPass;
   }
   if (generic_plan(p, gp)) return Path::kGeneric;
@@ -144,7 +167,7 @@ int xkv_decode(const xkv_decode_params* p, void* ws, size_t ws_bytes, void* stre
       return dense_tc_decode(*p, pl.dense, ws, st);
     case Path::kLatentTc:
       if (!ws || ws_bytes < pl.latent.total_bytes) return XKV_ERR_WORKSPACE;
-      return latent_tc_decode(*p, pl.latent, ws, st);
+      return latent_tc_decode(pl.rewritten, pl.latent, ws, st);
     case Path::kTwoPass:
       if (!ws || ws_bytes < pl.two_pass.total_bytes) return XKV_ERR_WORKSPACE;
       return two_pass_decode(p, 1, pl.two_pass, ws, st);

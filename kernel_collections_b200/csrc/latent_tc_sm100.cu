@@ -31,6 +31,9 @@ struct Args {
   const void* qeff;                     // [batch][H][dk], working dtype
   const float* logits;                  // FL mode: fp32 logits [b * lg_sb + h * lg_sh + token] from a first pass
   int64_t lg_sb, lg_sh;
+  void* logits_out;                     // logits-only mode: lo_scale * q_eff.k in the working dtype, no softmax / P.V
+  int64_t lo_sb, lo_sh;
+  float lo_scale;
   float* partial_o;                     // [batch][H][splits][rv]
   float* lse;                           // [batch][H][splits]
   int* status;
@@ -233,6 +236,27 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
           }
         }
       }
+      if (a.logits_out) {
+        // logits-only call: store the scaled scores and hand the stage back (no barriers in this mode)
+#pragma unroll
+        for (int u = 0; u < UPW; ++u) {
+          const int j = cw / MT + u * (NCW / MT);
+          const int tok = tile * TILE + j * 8 + 2 * t;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int h = h0 + mt_w * 16 + g + (i >> 1) * 8, tk = tok + (i & 1);
+            if (h < a.num_heads && tk < a.kv_len)
+              static_cast<T*>(a.logits_out)[(int64_t)b * a.lo_sb + (int64_t)h * a.lo_sh + tk] =
+                  TypeTraits<T>::from_f(sc[u][i] * a.lo_scale);
+          }
+        }
+        __syncwarp();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (lane == 0) mbar_arrive(bar_empty(stage));
+        if (++stage == a.stages) { stage = 0; phase ^= 1u; }
+        if (*abort_flag) break;
+        continue;
+      }
       // ---- tile max per head -------------------------------------------------------------------------
       float sv[UPW][4];
 #pragma unroll
@@ -336,7 +360,7 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     return;
   }
-  if (warp >= 1) {
+  if (warp >= 1 && a.logits_out == nullptr) {
     const float* lpart_s = reinterpret_cast<const float*>(sm + off_wmax);
     const int H = a.num_heads;
     const int nvt = a.rv / 64;
@@ -437,9 +461,25 @@ int dispatch(int hb, int nt, const CUtensorMap& tK, const CUtensorMap& tKt, cons
 
 }  // namespace
 
-bool latent_tc_supported(const xkv_decode_params& p) {
-  if (p.score_mode != XKV_SCORE_LATENT || p.value_mode != XKV_VALUE_LATENT) return false;
-  if (p.flags & XKV_FLAG_LOGITS_ONLY) return false;
+// A logits-only call is planned as if the values aliased the key latent: nothing but keys is streamed.
+static xkv_decode_params normalized(const xkv_decode_params& p) {
+  xkv_decode_params t = p;
+  if (p.flags & XKV_FLAG_LOGITS_ONLY) {
+    t.value_mode = XKV_VALUE_LATENT;
+    t.v = p.k; t.v_sl = p.k_sl; t.v_sb = p.k_sb;
+    t.v_rank = p.k_rank >= 128 ? 128 : p.k_rank;
+    t.v_proj = nullptr;
+    t.value_dim = t.v_rank;
+  }
+  return t;
+}
+
+bool latent_tc_supported(const xkv_decode_params& pin) {
+  if (pin.score_mode != XKV_SCORE_LATENT) return false;
+  const bool lo = (pin.flags & XKV_FLAG_LOGITS_ONLY) != 0;
+  if (!lo && pin.value_mode != XKV_VALUE_LATENT) return false;
+  if (lo && (pin.k_rank < 128 || (pin.lg_sh < pin.kv_len))) return false;
+  const xkv_decode_params p = normalized(pin);
   if (p.dtype != XKV_BF16 && p.dtype != XKV_F16) return false;
   if (p.logit_cap > 0.f) return false;
   if (p.k_rank % 64 != 0 || p.v_rank % 128 != 0 || p.tail_dim % 64 != 0) return false;
@@ -451,7 +491,8 @@ bool latent_tc_supported(const xkv_decode_params& p) {
   return smem_need(p, hb, 2) <= (size_t)MAX_SMEM;
 }
 
-bool latent_tc_plan(const xkv_decode_params& p, LatentTcPlan* pl) {
+bool latent_tc_plan(const xkv_decode_params& pin, LatentTcPlan* pl) {
+  const xkv_decode_params p = normalized(pin);
   const int hb = heads_per_cta(p);
   int stages = 4;
   while (stages > 2 && smem_need(p, hb, stages) > (size_t)MAX_SMEM) --stages;
@@ -483,7 +524,9 @@ bool latent_tc_plan(const xkv_decode_params& p, LatentTcPlan* pl) {
   return true;
 }
 
-int latent_tc_decode(const xkv_decode_params& p, const LatentTcPlan& pl, void* ws, cudaStream_t st) {
+int latent_tc_decode(const xkv_decode_params& pin, const LatentTcPlan& pl, void* ws, cudaStream_t st) {
+  const xkv_decode_params p = normalized(pin);
+  const bool lo = (pin.flags & XKV_FLAG_LOGITS_ONLY) != 0;
   char* w = static_cast<char*>(ws);
   const int dk = p.k_rank + p.tail_dim;
   const bool alias = p.v == p.k && p.v_sl == p.k_sl && p.v_sb == p.k_sb && p.v_rank <= p.k_rank;
@@ -520,10 +563,11 @@ int latent_tc_decode(const xkv_decode_params& p, const LatentTcPlan& pl, void* w
   const int hblocks = ceil_div(p.num_heads, pl.heads_per_cta);
   const int nt = p.v_rank / 64;
   a.logits = nullptr; a.lg_sb = a.lg_sh = 0;
+  a.logits_out = lo ? pin.logits : nullptr; a.lo_sb = pin.lg_sb; a.lo_sh = pin.lg_sh; a.lo_scale = pin.sm_scale;
   const int rc = p.dtype == XKV_BF16
                      ? dispatch<__nv_bfloat16, false>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st)
                      : dispatch<__half, false>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st);
-  if (rc != XKV_OK) return rc;
+  if (rc != XKV_OK || lo) return rc;
   return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, p.v_rank, p.value_dim,
                       p.v_proj, p.v_proj ? p.v_proj_heads : 1, p.vp_sb, p.vp_sh, p.vp_sr, p.vp_sd, p.o_sb, p.o_sh, st);
 }
@@ -584,6 +628,7 @@ int latent_pv_run(const xkv_decode_params& p, int heads, const LatentTcPlan& pl,
   a.num_splits = pl.num_splits; a.tiles_per_row = pl.tiles; a.stages = pl.stages;
   a.scale_log2 = 1.4426950408889634f;
   a.qeff = nullptr;
+  a.logits_out = nullptr; a.lo_sb = a.lo_sh = 0; a.lo_scale = 1.f;
   a.logits = logits; a.lg_sb = (int64_t)heads * p.kv_len; a.lg_sh = p.kv_len;
   a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
   a.lse = reinterpret_cast<float*>(w + pl.off_lse);

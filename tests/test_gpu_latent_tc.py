@@ -88,3 +88,50 @@ def test_mla(dtype, case):
     status_ok()
     close(got2, O.mla_absorbed(qq, qr, c[:, :, 0], kr[:, :, 0], Wk, Wv, sc), "mla_absorbed_decode (latent_tc)")
     assert torch.equal(got2, K.mla_absorbed_decode(qq.to(DEV), qrd, cd[:, :, 0], krd[:, :, 0], Wk.to(DEV), Wv.to(DEV), sc))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", [(2, 32, 576, 512, 1100), (1, 16, 320, 256, 70), (1, 128, 576, 512, 333)])
+def test_packed_single_kv_head_cache(dtype, case):
+    """The packed MLA layout of flash_decoding.mla (keys = [latent | rope], values = a prefix of the
+    keys, one KV head) is served by the shared-latent kernel; the aliased rows are read once."""
+    b, H, Dk, Dv, L = case
+    g = torch.Generator().manual_seed(43)
+    q = (torch.randn(b, H, Dk, generator=g) / 3).to(dtype)
+    kbuf = (torch.randn(b, L, 1, Dk, generator=g) / 3).to(dtype)
+    qd, kd = q.to(DEV), kbuf.to(DEV)
+    kw = dict(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, q=qd, k=kd, v=kd[..., :Dv], sm_scale=0.4)
+    assert ops.plan(**kw) == "latent_tc"
+    o = torch.zeros(b, H, Dv, dtype=dtype, device=DEV)
+    assert FD.mla.decode_attention_fwd(qd, kd, kd[..., :Dv], o, 0.4) is None
+    status_ok()
+    close(o, O.flash_decode_gqa(q, kbuf, kbuf[..., :Dv], 0.4), "packed MLA cache (latent_tc)")
+    # a separate value buffer of another width goes the same way
+    vbuf = (torch.randn(b, L, 1, 128, generator=g) / 3).to(dtype)
+    o2 = torch.zeros(b, H, 128, dtype=dtype, device=DEV)
+    FD.mla.decode_attention_fwd(qd, kd, vbuf.to(DEV), o2, 0.4)
+    close(o2, O.flash_decode_gqa(q, kbuf, vbuf, 0.4), "separate V buffer (latent_tc)")
+    # the logit cap is not covered by the fast kernel and must still be right
+    o3 = torch.zeros(b, H, Dv, dtype=dtype, device=DEV)
+    FD.mla.decode_attention_fwd(qd, kd, kd[..., :Dv], o3, 0.4, 3.0)
+    close(o3, O.flash_decode_gqa(q, kbuf, kbuf[..., :Dv], 0.4, logit_cap=3.0), "logit cap (portable)")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", [(2, 32, 8, 128, 1000, 256), (1, 64, 8, 128, 77, 128), (3, 8, 2, 64, 300, 512)])
+def test_qab_no_pe_logits(dtype, case):
+    """qAB without RoPE: absorbed logits q.(A.B)^T straight from the latent stream."""
+    b, H, kvh, D, L, R = case
+    g = torch.Generator().manual_seed(44)
+    q = torch.randn(b, H, 1, D, generator=g).to(dtype)
+    Ak = torch.randn(b, L, R, generator=g).to(dtype)
+    Bk = (torch.randn(b, kvh, R, D, generator=g) / R ** 0.5).to(dtype)
+    qd, Akd, Bkd = q.to(DEV), Ak.to(DEV), Bk.to(DEV)
+    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_DENSE, q=qd[:, :, 0], k=Akd, k_proj=Bkd,
+              logits_only=True, sm_scale=1.0)
+    assert ops.plan(**kw) == "latent_tc"
+    want = O.qab_no_pe(q, Ak, Bk)
+    for fn in (FR.qAB_no_pe_v1, FR.qAB_no_pe_v2, FR.qAB_no_pe_ref):
+        got = fn(qd, Akd, Bkd)
+        status_ok()
+        close(got, want, fn.__name__ if hasattr(fn, "__name__") else "qAB_no_pe")
