@@ -94,7 +94,7 @@ def w_group(reps):
 def w_group_kv(reps):
     """c3 as specified: 4 layers share the key latent AND the value latent (b32, L32768, R1024 each),
     per-layer B_k / B_v.  Two passes: grouped tcgen05 logits, then one P.A_v pass over 128 stacked heads."""
-    NL, b, H, KVH, D, L, R = 4, 32, 32, 8, 128, 32768, 1024
+    NL, b, H, KVH, D, L, R = 4, 32, 32, 8, 128, ctx(32768), 1024
     Ak, Av = rnd(b, L, R), rnd(b, L, R)
     qs = [rnd(b, H, 1, D) for _ in range(NL)]
     Bs = [rnd(R, KVH * D, scale=R ** -0.5) for _ in range(NL)]
@@ -108,7 +108,7 @@ def w_group_kv(reps):
 
 def w_v_only(reps):
     """c3, V-only-factorized variant: per layer dense K (b32, L32768) + the shared value latent (R1024)."""
-    b, H, KVH, D, L, R = 32, 32, 8, 128, 32768, 1024
+    b, H, KVH, D, L, R = 32, 32, 8, 128, ctx(32768), 1024
     q, k, Av = rnd(b, H, 1, D), rnd(b, L, KVH, D), rnd(b, L, R)
     Bv = rnd(b, KVH, R, D, scale=R ** -0.5)
     fn = lambda: A.group_query_attention_factorized_v_only(q, k.transpose(1, 2), Av, Bv)

@@ -294,7 +294,8 @@ template <typename T>
 __global__ void __launch_bounds__(NT)
 merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ lse, T* __restrict__ out,
              int num_heads, int heads_total, int head_offset, int S, int Dacc, int Dv, const T* __restrict__ v_proj, int v_div,
-             int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd, int64_t o_sb, int64_t o_sh) {
+             int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd, int64_t o_sb, int64_t o_sh,
+             int vec_proj) {
   extern __shared__ float smem[];
   float* w_s = smem;          // [S]
   float* o_s = smem + S;      // [Dacc]
@@ -344,6 +345,35 @@ merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ lse,
   T* orow = out + (int64_t)b * o_sb + (int64_t)h * o_sh;
   if (v_proj == nullptr) {
     for (int c = tid; c < Dacc; c += NT) stf(orow + c, o_s[c]);
+  } else if (vec_proj) {
+    // out[d] = sum_r o[r] * v_proj[r, d] with 16-byte loads: the threads form Dv / VEC column lanes
+    // times NT / lanes row groups; each group walks its share of the rank, the groups are then added
+    // in a fixed order.
+    constexpr int VEC = 16 / (int)sizeof(T);
+    __shared__ float part_s[NT * VEC];
+    const int lanes = Dv / VEC, groups = NT / lanes;
+    const int ln = tid % lanes, grp = tid / lanes;
+    float part[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) part[e] = 0.f;
+    const T* vp = v_proj + (int64_t)b * vp_sb + (int64_t)(h / v_div) * vp_sh + ln * VEC;
+    if (grp < groups) {
+      for (int r = grp; r < Dacc; r += groups) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(vp + (int64_t)r * vp_sr);
+        const T* e8 = reinterpret_cast<const T*>(&raw);
+        const float o = o_s[r];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) part[e] = fmaf(o, ldf(e8 + e), part[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) part_s[grp * Dv + ln * VEC + e] = part[e];
+    }
+    __syncthreads();
+    for (int d = tid; d < Dv; d += NT) {
+      float o = 0.f;
+      for (int k = 0; k < groups; ++k) o += part_s[k * Dv + d];
+      stf(orow + d, o);
+    }
   } else {
     const T* vp = v_proj + (int64_t)b * vp_sb + (int64_t)(h / v_div) * vp_sh;
     for (int d = tid; d < Dv; d += NT) {
@@ -500,11 +530,18 @@ int launch_merge(const float* partial_o, const float* lse, void* out, int dtype,
   if (smem > 40 * 1024) return XKV_ERR_UNSUPPORTED;
   const dim3 grid(num_heads, batch);
   const int div = v_proj ? num_heads / v_proj_heads : 1;
+  // vectorised projection: contiguous value columns, 16-byte aligned rows, lanes that divide the CTA
+  const int es = dtype == XKV_F32 ? 4 : 2, vec = 16 / es;
+  int vec_proj = 0;
+  if (v_proj && vp_sd == 1 && value_dim % vec == 0 && value_dim / vec <= NT && NT % (value_dim / vec) == 0 &&
+      (reinterpret_cast<uintptr_t>(v_proj) & 15u) == 0 && (vp_sr * es) % 16 == 0 && (vp_sh * es) % 16 == 0 &&
+      (vp_sb * es) % 16 == 0)
+    vec_proj = 1;
 #define XKV_MERGE(T)                                                                                  \
   merge_kernel<T><<<grid, NT, smem, st>>>(partial_o, lse, static_cast<T*>(out), num_heads, heads_total, \
                                           head_offset, num_splits,                                  \
                                           acc_dim, value_dim, static_cast<const T*>(v_proj), div, vp_sb, \
-                                          vp_sh, vp_sr, vp_sd, o_sb, o_sh)
+                                          vp_sh, vp_sr, vp_sd, o_sb, o_sh, vec_proj)
   switch (dtype) {
     case XKV_F32: XKV_MERGE(float); break;
     case XKV_BF16: XKV_MERGE(__nv_bfloat16); break;

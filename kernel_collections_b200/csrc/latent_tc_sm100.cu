@@ -399,10 +399,21 @@ __global__ void absorb_query_lowp_kernel(const xkv_decode_params p, T* __restric
   if (p.k_proj != nullptr) {
     const int div = p.num_heads / p.k_proj_heads;
     const T* kp = static_cast<const T*>(p.k_proj) + (int64_t)b * p.kp_sb + (int64_t)(h / div) * p.kp_sh;
+    const bool vec = p.kp_sd == 1 && p.head_dim % 8 == 0 && (reinterpret_cast<uintptr_t>(kp) & 15u) == 0 &&
+                     (p.kp_sr * 2) % 16 == 0;
     for (int r = threadIdx.x; r < p.k_rank; r += blockDim.x) {
       const T* rowp = kp + (int64_t)r * p.kp_sr;
       float s = 0.f;
-      for (int d = 0; d < p.head_dim; ++d) s = fmaf(q_s[d], TypeTraits<T>::to_f(rowp[(int64_t)d * p.kp_sd]), s);
+      if (vec) {
+        for (int d = 0; d < p.head_dim; d += 8) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(rowp + d);
+          const T* e8 = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s = fmaf(q_s[d + e], TypeTraits<T>::to_f(e8[e]), s);
+        }
+      } else {
+        for (int d = 0; d < p.head_dim; ++d) s = fmaf(q_s[d], TypeTraits<T>::to_f(rowp[(int64_t)d * p.kp_sd]), s);
+      }
       out[r] = TypeTraits<T>::from_f(s);
     }
   } else {
