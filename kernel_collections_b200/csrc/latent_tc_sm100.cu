@@ -86,7 +86,7 @@ __device__ __forceinline__ bool group_bar_aborted(volatile int* abort_flag) {
 // FL: the scores come as fp32 logits from a first pass (reconstructed or dense keys) instead of
 //     Q_eff . K^T; only the value latent is streamed.
 template <typename T, int HB, int NT, bool FL>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(NTHREADS, (HB == 32 && NT <= 4) ? 2 : 1)
 latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmKt,
                  const __grid_constant__ CUtensorMap tmV, const Args a) {
   constexpr int MT = HB / 16;                       // m-tiles of 16 heads
@@ -305,13 +305,19 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
       }
       group_bar();                                  // (B) P visible
       // ---- O = O * alpha + P . V : this warp owns value columns [cw * rv/8, (cw+1) * rv/8) -----------
+      // the running maxima settle after the first tiles: skip the rescale while no row of the warp moved
+      bool moved = false;
 #pragma unroll
-      for (int m = 0; m < MT; ++m)
+      for (int m = 0; m < MT; ++m) moved = moved || alpha[m][0] != 1.f || alpha[m][1] != 1.f;
+      if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          acc[m][n][0] *= alpha[m][0]; acc[m][n][1] *= alpha[m][0];
-          acc[m][n][2] *= alpha[m][1]; acc[m][n][3] *= alpha[m][1];
-        }
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+            acc[m][n][0] *= alpha[m][0]; acc[m][n][1] *= alpha[m][0];
+            acc[m][n][2] *= alpha[m][1]; acc[m][n][3] *= alpha[m][1];
+          }
+      }
 #pragma unroll
       for (int ks = 0; ks < TILE / 16; ++ks) {
         uint32_t pa[MT][4];
@@ -506,13 +512,17 @@ bool latent_tc_plan(const xkv_decode_params& pin, LatentTcPlan* pl) {
   const xkv_decode_params p = normalized(pin);
   const int hb = heads_per_cta(p);
   int stages = 4;
-  while (stages > 2 && smem_need(p, hb, stages) > (size_t)MAX_SMEM) --stages;
+  // the small variant (32 heads, value rank <= 256) is compiled for two CTAs per SM: keep its
+  // footprint under half of the shared memory when two stages allow it
+  const size_t budget = (hb == 32 && p.v_rank <= 256 && smem_need(p, hb, 2) <= (size_t)MAX_SMEM / 2)
+                            ? (size_t)MAX_SMEM / 2 - 1024 : (size_t)MAX_SMEM;
+  while (stages > 2 && smem_need(p, hb, stages) > budget) --stages;
   pl->heads_per_cta = hb;
   pl->stages = stages;
   pl->smem_bytes = smem_need(p, hb, stages) + 1024;
   const int tiles = ceil_div(p.kv_len, TILE);
   const int rows = p.batch * ceil_div(p.num_heads, hb);
-  const int sms = device_sm_count();
+  const int sms = device_sm_count() * (budget < (size_t)MAX_SMEM ? 2 : 1);   // CTA slots
   int best_s = 1;
   int64_t best_cost = -1;
   const int max_s = tiles < 64 ? tiles : 64;
