@@ -18,6 +18,7 @@
 // it gave up in the status words of the workspace, lets every role drain to the common exit,
 // waits for copies in flight, frees its TMEM and returns.  No TMA load uses cluster multicast.
 #include "sm100_common.cuh"
+#include <stdlib.h>
 
 namespace xkv {
 using namespace sm100;
@@ -48,7 +49,7 @@ constexpr int OFF_WMAX = OFF_P + 2 * P_BUF;                      // 229888
 constexpr int OFF_ALPHA = OFF_WMAX + 2 * 4 * 16 * 4;             // +512
 constexpr int OFF_M = OFF_ALPHA + 2 * 16 * 4;                    // +128
 constexpr int OFF_BAR = OFF_M + 64 * 4;                          // +256
-constexpr int NUM_BARS = 2 * STAGES + 4 + 4 + 4;
+constexpr int NUM_BARS = 20;   // full[4] empty[4] tfull[2] tempty[2] vfull[2] vempty[2] pfull[2] pempty[2]
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
 constexpr int OFF_FREQ = OFF_MISC + 16;                          // 64 RoPE frequencies
 constexpr int SMEM_USED = OFF_FREQ + 64 * 4;
@@ -118,6 +119,54 @@ __device__ __forceinline__ bool epilogue_sync_aborted(volatile int* abort_flag) 
       : "memory");
   return any != 0;
 }
+// ---- thread-block-cluster helpers for the CTA-pair (cta_group::2) variant -----------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local_addr` (an address in this CTA's shared window) in CTA `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA loads of the pair variant: the data lands in this CTA, the bytes are counted on the mbarrier
+// of the leader CTA (`bar` is a shared::cluster address).  No multicast: each CTA fetches its own.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                                 uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                                 uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -166,7 +215,24 @@ __device__ __forceinline__ void sincos_reduced(float x, float& sn, float& cs) {
 }
 
 // ---------------------------------------------------------------------------------------------
-template <typename T, int G, bool LOGITS_ONLY>
+// PAIR: two CTAs of a cluster share every MMA (tcgen05 cta_group::2, M = 256): each loads its own
+// 128-token latent tile and HALF of the B chunk (one KV head), the leader CTA issues the MMAs, and
+// each CTA finds the keys of its own tokens for both KV heads in its own TMEM.  This halves the B
+// bytes written to and read from shared memory, the unit that paces the 1-CTA kernel.  Everything
+// after the accumulators (epilogue, V ring, P.V) is per CTA and unchanged.
+// Two angles at a time on the packed fp32x2 pipe (Blackwell): same Cody-Waite steps, element-wise
+// IEEE products and FMAs, then the SFU approximations per element.
+__device__ __forceinline__ void sincos_reduced2(float2 x, float2& sn, float2& cs) {
+  const float2 magic = make_float2(12582912.0f, 12582912.0f), nmagic = make_float2(-12582912.0f, -12582912.0f);
+  const float2 k = __fadd2_rn(__ffma2_rn(x, make_float2(0.15915494309189535f, 0.15915494309189535f), magic), nmagic);
+  float2 r = __ffma2_rn(k, make_float2(-6.28125f, -6.28125f), x);
+  r = __ffma2_rn(k, make_float2(-1.9350051879882812e-3f, -1.9350051879882812e-3f), r);
+  r = __ffma2_rn(k, make_float2(-3.019916050561733e-7f, -3.019916050561733e-7f), r);
+  sn = make_float2(__sinf(r.x), __sinf(r.y));
+  cs = make_float2(__cosf(r.x), __cosf(r.y));
+}
+
+template <typename T, int G, bool LOGITS_ONLY, bool PAIR>
 __global__ void __launch_bounds__(NTHREADS, 1)
 recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
   extern __shared__ uint8_t smem_raw[];
@@ -178,32 +244,44 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
   // The layer index varies fastest over the grid: the CTAs of one (split, batch row) that serve
   // the layers of a group are scheduled together and stream the same latent tiles, which are then
   // read from HBM once and served from L2 to the other layers.
-  const int layer = blockIdx.x % a.num_layers, split = blockIdx.x / a.num_layers, b = blockIdx.y;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;           // 0 = leader of the pair
+  const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int layer = unit % a.num_layers, split = unit / a.num_layers, b = blockIdx.y;
   const CUtensorMap* tmA = &maps.a;
   const CUtensorMap* tmB = &maps.b[layer];
   const CUtensorMap* tmV = &maps.v[layer];
   const int64_t row = (int64_t)layer * a.batch + b;   // row of the partial / lse buffers
-  const int tile_begin = (int)(((int64_t)split * a.tiles_per_row) / a.num_splits);
-  const int tile_end = (int)(((int64_t)(split + 1) * a.tiles_per_row) / a.num_splits);
+  // tiles [range_begin, range_end) belong to this split; a pair interleaves them (leader even, peer
+  // odd positions) and both CTAs run the same number of iterations, the peer possibly ending on
+  // a phantom tile whose tokens are all masked
+  const int range_begin = (int)(((int64_t)split * a.tiles_per_row) / a.num_splits);
+  const int range_end = (int)(((int64_t)(split + 1) * a.tiles_per_row) / a.num_splits);
+  constexpr int TSTEP = PAIR ? 2 : 1;
+  const int tile_begin = range_begin + (int)rank;
+  const int tile_end = PAIR ? tile_begin + 2 * ((range_end - range_begin + 1) / 2) : range_end;
+  const int out_split = PAIR ? split * 2 + (int)rank : split;       // slot of the partial / lse buffers
+  const int out_splits = PAIR ? a.num_splits * 2 : a.num_splits;
   const int KB = a.rank / BK;
+  constexpr int NSTAGE = PAIR ? 4 : STAGES;                          // the pair's stages are 32 KB
+  constexpr int STAGE_SZ = PAIR ? A_BYTES + B_BYTES / 2 : STAGE_BYTES;
 
   const uint32_t bar0 = base + OFF_BAR;
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
-  auto bar_empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  auto bar_tfull = [&](int i) { return bar0 + 8u * (2 * STAGES + i); };
-  auto bar_tempty = [&](int i) { return bar0 + 8u * (2 * STAGES + 2 + i); };
-  auto bar_vfull = [&](int i) { return bar0 + 8u * (2 * STAGES + 4 + i); };
-  auto bar_vempty = [&](int i) { return bar0 + 8u * (2 * STAGES + 6 + i); };
-  auto bar_pfull = [&](int i) { return bar0 + 8u * (2 * STAGES + 8 + i); };
-  auto bar_pempty = [&](int i) { return bar0 + 8u * (2 * STAGES + 10 + i); };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (4 + s); };
+  auto bar_tfull = [&](int i) { return bar0 + 8u * (8 + i); };
+  auto bar_tempty = [&](int i) { return bar0 + 8u * (10 + i); };
+  auto bar_vfull = [&](int i) { return bar0 + 8u * (12 + i); };
+  auto bar_vempty = [&](int i) { return bar0 + 8u * (14 + i); };
+  auto bar_pfull = [&](int i) { return bar0 + 8u * (16 + i); };
+  auto bar_pempty = [&](int i) { return bar0 + 8u * (18 + i); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 4);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_tfull(i), 1);
-      mbar_init(bar_tempty(i), 128);
+      mbar_init(bar_tempty(i), PAIR ? 256 : 128);   // the leader also collects the peer's epilogue
       mbar_init(bar_vfull(i), 1);
       mbar_init(bar_vempty(i), 128);
       mbar_init(bar_pfull(i), 128);
@@ -214,8 +292,13 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + OFF_MISC), "r"(512u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {   // both CTAs of the pair issue the allocation, same warp, same destination offset
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + OFF_MISC), "r"(512u) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + OFF_MISC), "r"(512u) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   if (threadIdx.x >= 128 && threadIdx.x < 256) {   // running maxima start at -inf
     float* m_s = reinterpret_cast<float*>(sm + OFF_M);
@@ -228,6 +311,7 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything is signalled across CTAs
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 #ifdef XKV_TC_PROFILE
@@ -240,20 +324,30 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
       int stage = 0;
       uint32_t phase = 0;
       const int bb = a.b_batched ? b : 0;
-      for (int tile = tile_begin; tile < tile_end; ++tile) {
+      for (int tile = tile_begin; tile < tile_end; tile += TSTEP) {
         for (int c = 0; c < NCH; ++c) {
           for (int kb = 0; kb < KB; ++kb) {
             if (!XKV_PROF_WAIT(0, mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag))) {
               report(a.status, XKV_ERR_TIMEOUT, 0, tile, c, kb);
               goto producer_done;
             }
-            mbar_expect_tx(bar_full(stage), STAGE_BYTES);
-            const uint32_t sa = base + OFF_STAGE + stage * STAGE_BYTES;
-            tma_load_3d(sa, tmA, kb * BK, tile * TILE_M, b, bar_full(stage));
+            const uint32_t sa = base + OFF_STAGE + stage * STAGE_SZ;
+            if (PAIR) {
+              // bytes of both CTAs are counted on the leader's barrier, which the leader arms for both
+              const uint32_t lead_full = map_to_cta(bar_full(stage), 0);
+              if (rank == 0) mbar_expect_tx(bar_full(stage), 2 * STAGE_SZ);
+              tma_load_3d_pair(sa, tmA, kb * BK, tile * TILE_M, b, lead_full);
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              tma_load_4d(sa + A_BYTES + i * B_BOX, tmB, (i & 1) * 64, kb * BK, 2 * c + (i >> 1), bb, bar_full(stage));
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+              for (int i = 0; i < 2; ++i)   // this CTA's half of the chunk: KV head 2c + rank
+                tma_load_4d_pair(sa + A_BYTES + i * B_BOX, tmB, i * 64, kb * BK, 2 * c + (int)rank, bb, lead_full);
+            } else {
+              mbar_expect_tx(bar_full(stage), STAGE_BYTES);
+              tma_load_3d(sa, tmA, kb * BK, tile * TILE_M, b, bar_full(stage));
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                tma_load_4d(sa + A_BYTES + i * B_BOX, tmB, (i & 1) * 64, kb * BK, 2 * c + (i >> 1), bb, bar_full(stage));
+            }
+            if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
           }
         }
       }
@@ -261,13 +355,13 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
   producer_done:;
   } else if (warp == 1) {
     // =========================== MMA issuer ===================================================
-    if (lane == 0) {
-      // instruction descriptor: fp32 accumulate, A K-major, B MN-major, N = 256, M = 128
+    if (lane == 0 && rank == 0) {   // in a pair only the leader issues
+      // instruction descriptor: fp32 accumulate, A K-major, B MN-major, N = 256, M = 128 (256 for a pair)
       const uint32_t idesc = (1u << 4) | (TypeTraits<T>::kFmt << 7) | (TypeTraits<T>::kFmt << 10) | (1u << 16) |
-                             ((256u >> 3) << 17) | ((128u >> 4) << 24);
+                             ((256u >> 3) << 17) | (((PAIR ? 256u : 128u) >> 4) << 24);
       int stage = 0, abuf = 0;
       uint32_t phase = 0, aphase = 0;
-      for (int tile = tile_begin; tile < tile_end; ++tile) {
+      for (int tile = tile_begin; tile < tile_end; tile += TSTEP) {
         for (int c = 0; c < NCH; ++c) {
           if (!XKV_PROF_WAIT(1, mbar_wait(bar_tempty(abuf), aphase ^ 1u, abort_flag))) {
             report(a.status, XKV_ERR_TIMEOUT, 1, tile, c, -1);
@@ -281,17 +375,28 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
               goto mma_done;
             }
             tc_fence_after();
-            const uint32_t sa = base + OFF_STAGE + stage * STAGE_BYTES;
+            const uint32_t sa = base + OFF_STAGE + stage * STAGE_SZ;
 #pragma unroll
             for (int k4 = 0; k4 < BK / 16; ++k4) {
               const uint64_t da = smem_desc(sa + k4 * 32, 16, 1024);
               const uint64_t db = smem_desc(sa + A_BYTES + k4 * 2048, B_BOX, 1024);
-              tc_mma(tacc, da, db, idesc, (kb | k4) != 0 ? 1u : 0u);
+              if (PAIR) tc_mma_pair(tacc, da, db, idesc, (kb | k4) != 0 ? 1u : 0u);
+              else tc_mma(tacc, da, db, idesc, (kb | k4) != 0 ? 1u : 0u);
             }
-            tc_commit(bar_empty(stage));
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            if (PAIR) {   // free the stage in both CTAs (two plain commits, one per CTA)
+              tc_commit_pair(map_to_cta(bar_empty(stage), 0));
+              tc_commit_pair(map_to_cta(bar_empty(stage), 1));
+            } else {
+              tc_commit(bar_empty(stage));
+            }
+            if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
           }
-          tc_commit(bar_tfull(abuf));
+          if (PAIR) {
+            tc_commit_pair(map_to_cta(bar_tfull(abuf), 0));
+            tc_commit_pair(map_to_cta(bar_tfull(abuf), 1));
+          } else {
+            tc_commit(bar_tfull(abuf));
+          }
           abuf ^= 1;
           if (abuf == 0) aphase ^= 1u;
         }
@@ -303,7 +408,7 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
     if (!LOGITS_ONLY && lane == 0) {
       int slot = 0;
       uint32_t ph = 0;
-      for (int tile = tile_begin; tile < tile_end; ++tile) {
+      for (int tile = tile_begin; tile < tile_end; tile += TSTEP) {
         for (int kvh = 0; kvh < KVH; ++kvh) {
           if (!XKV_PROF_WAIT(3, mbar_wait(bar_vempty(slot), ph ^ 1u, abort_flag))) {
             report(a.status, XKV_ERR_TIMEOUT, 2, tile, kvh, -1);
@@ -344,9 +449,9 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
       }
     };
     q_fetch(0);
-    for (int tile = tile_begin; tile < tile_end; ++tile) {
+    for (int tile = tile_begin; tile < tile_end; tile += TSTEP) {
       const int tok = tile * TILE_M + et;
-      const bool valid = tok < a.kv_len;
+      const bool valid = tok < a.kv_len && tile < range_end;   // (a pair's peer may end on a phantom tile)
       const float pos_f = (float)(a.pos_offset + tok);
       for (int c = 0; c < NCH; ++c) {
         // ---- stage this chunk's queries: q_s[hh][j][g][{j, j+64}] = q * scale -----------------
@@ -359,7 +464,9 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int d = d0 + e;
-            q_s[((hh * 64 + (d & 63)) * G + g) * 2 + (d >> 6)] = TypeTraits<T>::to_f(e8[e]) * a.q_scale;
+            // pairs of frequencies side by side: [hh][j / 2][g][{x_j, x_j+1, y_j, y_j+1}], x = dim j, y = dim j + 64
+            const int j = d & 63;
+            q_s[((hh * 32 + (j >> 1)) * G + g) * 4 + (d >> 6) * 2 + (j & 1)] = TypeTraits<T>::to_f(e8[e]) * a.q_scale;
           }
         }
         q_fetch((c + 1) % NCH);
@@ -372,15 +479,21 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
         if (!XKV_PROF_WAIT_L(4, et == 0, mbar_wait(bar_tfull(abuf), aphase, abort_flag))) report(a.status, XKV_ERR_TIMEOUT, 4, tile, c, 0);
         tc_fence_after();
 
-        float s[2 * G];
+        // logits accumulate on the packed fp32x2 pipe: lane .x holds the even frequencies, .y the odd
+        float2 s2[2 * G];
 #pragma unroll
-        for (int i = 0; i < 2 * G; ++i) s[i] = 0.f;
+        for (int i = 0; i < 2 * G; ++i) s2[i] = make_float2(0.f, 0.f);
+        const float2 pos2 = make_float2(pos_f, pos_f);
 #pragma unroll 1
         for (int jb = 0; jb < 4; ++jb) {
           // rotation of this token for frequencies jb*16 .. jb*16+15, shared by both KV heads
-          float cs[16], sn[16];
+          float2 cs[8], sn[8], nsn[8];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) sincos_reduced(__fmul_rn(pos_f, freq_s[jb * 16 + i]), sn[i], cs[i]);
+          for (int i = 0; i < 8; ++i) {
+            const float2 f2 = *reinterpret_cast<const float2*>(freq_s + jb * 16 + 2 * i);
+            sincos_reduced2(__fmul2_rn(pos2, f2), sn[i], cs[i]);
+            nsn[i] = make_float2(-sn[i].x, -sn[i].y);
+          }
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
             uint32_t x0[16], x1[16];
@@ -389,21 +502,27 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
             tmem_ld16(lane_addr + col + 64, x1);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float k0 = __uint_as_float(x0[i]), k1 = __uint_as_float(x1[i]);
-              const float r0 = k0 * cs[i] - k1 * sn[i];
-              const float r1 = k1 * cs[i] + k0 * sn[i];
-              const float2* qp = reinterpret_cast<const float2*>(q_s + ((hh * 64 + jb * 16 + i) * G) * 2);
+            for (int i = 0; i < 8; ++i) {
+              const float2 k0 = make_float2(__uint_as_float(x0[2 * i]), __uint_as_float(x0[2 * i + 1]));
+              const float2 k1 = make_float2(__uint_as_float(x1[2 * i]), __uint_as_float(x1[2 * i + 1]));
+              const float2 r0 = __ffma2_rn(k0, cs[i], __fmul2_rn(k1, nsn[i]));
+              const float2 r1 = __ffma2_rn(k1, cs[i], __fmul2_rn(k0, sn[i]));
+              const float4* qp = reinterpret_cast<const float4*>(q_s + ((hh * 32 + jb * 8 + i) * G) * 4);
 #pragma unroll
               for (int g = 0; g < G; ++g) {
-                const float2 qq = qp[g];
-                s[hh * G + g] = fmaf(qq.x, r0, fmaf(qq.y, r1, s[hh * G + g]));
+                const float4 qq = qp[g];
+                s2[hh * G + g] = __ffma2_rn(make_float2(qq.x, qq.y), r0,
+                                            __ffma2_rn(make_float2(qq.z, qq.w), r1, s2[hh * G + g]));
               }
             }
           }
         }
+        float s[2 * G];
+#pragma unroll
+        for (int i = 0; i < 2 * G; ++i) s[i] = s2[i].x + s2[i].y;
         tc_fence_before();
-        mbar_arrive(bar_tempty(abuf));
+        if (PAIR && rank != 0) mbar_arrive_cluster(map_to_cta(bar_tempty(abuf), 0));   // the leader issues the MMAs
+        else mbar_arrive(bar_tempty(abuf));
         abuf ^= 1;
         if (abuf == 0) aphase ^= 1u;
 
@@ -431,24 +550,26 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
             if (lane == 0) wmax_s[(par * 4 + ew) * 16 + i] = wm;
           }
           if (epilogue_sync_aborted(abort_flag)) goto epi_done;
-          float m_new[2 * G];
+          float m_new[2 * G], m_use[2 * G];
 #pragma unroll
           for (int i = 0; i < 2 * G; ++i) {
             float mx = m_old[i];
 #pragma unroll
             for (int w = 0; w < 4; ++w) mx = fmaxf(mx, wmax_s[(par * 4 + w) * 16 + i]);
             m_new[i] = mx;
+            if (mx == -CUDART_INF_F) mx = 0.f;   // nothing seen yet (phantom tile): keep exp2 finite
+            m_use[i] = mx;
           }
           par ^= 1;
           if (!XKV_PROF_WAIT_L(5, et == 0, mbar_wait(bar_pempty(pbuf), pphase ^ 1u, abort_flag))) report(a.status, XKV_ERR_TIMEOUT, 4, tile, c, 1);
           T* p_s = reinterpret_cast<T*>(sm + OFF_P + pbuf * P_BUF);
 #pragma unroll
           for (int i = 0; i < 2 * G; ++i)
-            p_s[i * (P_PITCH / 2) + et] = TypeTraits<T>::from_f(exp2f(s[i] - m_new[i]));
+            p_s[i * (P_PITCH / 2) + et] = TypeTraits<T>::from_f(exp2f(s[i] - m_use[i]));
           if (et == 0) {
 #pragma unroll
             for (int i = 0; i < 2 * G; ++i) {
-              alpha_s[pbuf * 16 + i] = exp2f(m_old[i] - m_new[i]);
+              alpha_s[pbuf * 16 + i] = exp2f(m_old[i] - m_use[i]);
               m_s[c * 2 * G + i] = m_new[i];
             }
           }
@@ -478,7 +599,7 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
       int slot = 0, pbuf = 0;
       uint32_t vph = 0, pph = 0;
       bool alive = true;
-      for (int tile = tile_begin; tile < tile_end && alive; ++tile) {
+      for (int tile = tile_begin; tile < tile_end && alive; tile += TSTEP) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
           bool ok = XKV_PROF_WAIT_L(6, threadIdx.x == 256, mbar_wait(bar_pfull(pbuf), pph, abort_flag));
@@ -556,7 +677,7 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
               const int h = kvh * G + hd;
               const float l = lacc[kvh][n];
               const float inv = l > 0.f ? 1.f / l : 0.f;
-              float* po = a.partial_o + ((row * H + h) * a.num_splits + split) * D;
+              float* po = a.partial_o + ((row * H + h) * out_splits + out_split) * D;
 #pragma unroll
               for (int mt = 0; mt < 2; ++mt) {
                 const int dim = pw * 32 + mt * 16 + g;
@@ -564,7 +685,7 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
                 po[dim + 8] = acc[kvh][mt][2 + n] * inv;
               }
               if (pw == 0 && g == 0)
-                a.lse[(row * H + h) * a.num_splits + split] =
+                a.lse[(row * H + h) * out_splits + out_split] =
                     l > 0.f ? (m_s[h] + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
             }
           }
@@ -590,21 +711,48 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
     // memory and TMEM are released
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
+  if (PAIR) {
+    // neither CTA leaves (or frees TMEM) while the other may still signal its barriers or have MMAs
+    // reading its shared memory
+    tc_fence_before();
+    cluster_sync_all();
+  }
   if (warp == 2) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
-template <typename T, int G, bool LO>
-int launch(const TensorMaps& maps, const Args& args, cudaStream_t st) {
-  auto kern = recon_tc_kernel<T, G, LO>;
+template <typename T, int G, bool LO, bool PAIR>
+int launch_variant(const TensorMaps& maps, const Args& args, cudaStream_t st) {
+  auto kern = recon_tc_kernel<T, G, LO, PAIR>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
     cudaGetLastError();
     return XKV_ERR_LAUNCH;
   }
-  kern<<<dim3(args.num_splits * args.num_layers, args.batch), NTHREADS, SMEM_BYTES, st>>>(maps, args);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(args.num_splits * args.num_layers * (PAIR ? 2 : 1), args.batch);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = PAIR ? 2 : 1;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, maps, args) != cudaSuccess) {
+    cudaGetLastError();
+    return XKV_ERR_LAUNCH;
+  }
   return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
+}
+
+template <typename T, int G, bool LO>
+int launch(const TensorMaps& maps, const Args& args, bool pair, cudaStream_t st) {
+  return pair ? launch_variant<T, G, LO, true>(maps, args, st) : launch_variant<T, G, LO, false>(maps, args, st);
 }
 
 }  // namespace
@@ -646,18 +794,43 @@ static int choose_splits(int rows, int tiles) {
   return best_s;
 }
 
+// Whether the CTA-pair (cta_group::2) variant serves a call.  It is parity-tested but measured no
+// faster than single CTAs while the epilogue paces the kernel (halving the B traffic does not
+// shorten the critical path), so it is opt-in: XKV_RECON_PAIR=1, and at least two tiles per row.
+static bool want_pair(int tiles) {
+  const char* e = getenv("XKV_RECON_PAIR");
+  return e != nullptr && e[0] == '1' && tiles >= 2;
+}
+
 static bool plan_layers(const xkv_decode_params& p, int num_layers, ReconTcPlan* pl) {
   const int tiles = ceil_div(p.kv_len, TILE_M);
-  pl->num_splits = choose_splits(p.batch * num_layers, tiles);
+  const int rows = p.batch * num_layers;
+  pl->pair = want_pair(tiles) ? 1 : 0;
+  if (pl->pair) {
+    // splits are served by pairs of CTAs: SMs / 2 slots, each slot works through ceil(tiles / 2) rounds
+    const int slots = device_sm_count() / 2;
+    int best_s = 1;
+    int64_t best_cost = -1;
+    const int max_s = tiles / 2 < 64 ? tiles / 2 : 64;
+    for (int s = 1; s <= max_s; ++s) {
+      const int64_t waves = ceil_div(rows * s, slots);
+      const int64_t cost = waves * ceil_div(ceil_div(tiles, s), 2);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = s; }
+    }
+    pl->num_splits = best_s;
+  } else {
+    pl->num_splits = choose_splits(rows, tiles);
+  }
   pl->tiles_per_split = tiles;   // tiles per batch row; the kernel cuts [s*T/S, (s+1)*T/S)
+  const int out_splits = pl->num_splits * (pl->pair ? 2 : 1);
   size_t off = 256;              // status words
   pl->off_table = off;
   pl->off_partial = off;
   const bool lo = (p.flags & XKV_FLAG_LOGITS_ONLY) != 0;
-  const size_t rows = (size_t)num_layers * p.batch * p.num_heads * pl->num_splits;
-  if (!lo) off += align_up(rows * D * sizeof(float), 256);
+  const size_t nrows = (size_t)num_layers * p.batch * p.num_heads * out_splits;
+  if (!lo) off += align_up(nrows * D * sizeof(float), 256);
   pl->off_lse = off;
-  if (!lo) off += align_up(rows * sizeof(float), 256);
+  if (!lo) off += align_up(nrows * sizeof(float), 256);
   pl->total_bytes = off;
   return true;
 }
@@ -750,7 +923,7 @@ int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcP
   a.b_batched = b_batched;
 
   int rc;
-#define XKV_TC(T, GG) rc = lo ? launch<T, GG, true>(maps, a, st) : launch<T, GG, false>(maps, a, st)
+#define XKV_TC(T, GG) rc = lo ? launch<T, GG, true>(maps, a, pl.pair != 0, st) : launch<T, GG, false>(maps, a, pl.pair != 0, st)
   if (p.dtype == XKV_BF16) {
     if (G == 4) { XKV_TC(__nv_bfloat16, 4); } else { XKV_TC(__nv_bfloat16, 8); }
   } else {
@@ -759,10 +932,11 @@ int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcP
 #undef XKV_TC
   if (rc != XKV_OK) return rc;
   if (lo) return XKV_OK;
-  const size_t layer_rows = (size_t)p.batch * p.num_heads * pl.num_splits;
+  const int out_splits = pl.num_splits * (pl.pair ? 2 : 1);
+  const size_t layer_rows = (size_t)p.batch * p.num_heads * out_splits;
   for (int i = 0; i < n; ++i) {
     rc = launch_merge(a.partial_o + i * layer_rows * D, a.lse + i * layer_rows, layers[i].out, p.dtype, p.batch,
-                      p.num_heads, pl.num_splits, D, D, nullptr, 1, 0, 0, 0, 0, layers[i].o_sb, layers[i].o_sh, st);
+                      p.num_heads, out_splits, D, D, nullptr, 1, 0, 0, 0, 0, layers[i].o_sb, layers[i].o_sh, st);
     if (rc != XKV_OK) return rc;
   }
   return XKV_OK;

@@ -40,7 +40,8 @@ int launch_rope_table(float* cos_sin, int kv_len, int half, int pos_offset, floa
 
 // ---- tcgen05 key-reconstruction path (recon_tc_sm100.cu) ------------------------------------
 struct ReconTcPlan {
-  int num_splits;       // CTAs per batch row
+  int pair;             // CTA pairs (cta_group::2) instead of single CTAs
+  int num_splits;       // CTAs (or CTA pairs) per batch row
   int tiles_per_split;  // 128-token tiles per CTA
   size_t off_table, off_partial, off_lse, total_bytes;
 };
