@@ -2,9 +2,9 @@
 // scores the same rows A[b, l, :] (+ a decoupled RoPE tail) and accumulates the same value rows, so
 // the heads are the M dimension of the MMAs and the latent is streamed exactly once per head block.
 //
-// One CTA per (KV split, block of HB heads, batch row).  Warp 0 is the TMA producer: 32-token
+// One CTA per (KV split, block of HB heads, batch row), eight warps.  A TMA ring holds 32-token
 // tiles of the key latent (64-column, 128-byte-swizzled blocks), the tail and, unless the values
-// alias the key latent (MLA), the value latent.  Warps 1-8 compute:
+// alias the key latent (MLA), the value latent; the last warp to finish a stage refills it.  Per tile:
 //   S[HB x 32] = Q_eff . K_tile^T   split into (16 heads x 8 tokens) units over the warps, Q_eff
 //                                   (bf16, HB x Dk) resident in shared memory, ldmatrix operands
 //   tile max per head through shared memory, P = exp2(S - m) -> shared memory (bf16)
@@ -19,7 +19,7 @@ namespace {
 
 constexpr int TILE = 32;                // tokens per stage
 constexpr int NCW = 8;                  // compute warps
-constexpr int NTHREADS = 32 * (NCW + 1);
+constexpr int NTHREADS = 32 * NCW;      // no producer warp: the last warp to finish a stage refills it
 constexpr int MAX_SMEM = 232448 - 1024;
 
 struct Args {
@@ -117,11 +117,11 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   const uint32_t off_l = off_wmax + HB * 16;                    // [HB] floats
   const uint32_t off_bar = off_l + HB * 4;
   auto bar_full = [&](int s) { return base + off_bar + 8u * s; };
-  auto bar_empty = [&](int s) { return base + off_bar + 8u * (4 + s); };
+  int* cnt_s = reinterpret_cast<int*>(sm + off_bar + 32);      // per stage: warps that finished reading it
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + off_bar + 64);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < a.stages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), NCW); }
+    for (int s = 0; s < a.stages; ++s) { mbar_init(bar_full(s), 1); cnt_s[s] = 0; }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -149,29 +149,36 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 #pragma unroll
   for (int m = 0; m < MT; ++m) { m_run[m][0] = -CUDART_INF_F; m_run[m][1] = -CUDART_INF_F; }
   float l_run[2] = {0.f, 0.f};
-  const int cw = warp - 1;                          // compute warp index (warp 0 is the producer)
+  const int cw = warp;                              // all eight warps compute
   const int mt_w = cw % MT;                         // the m-tile all score units of this warp belong to
 
-  if (warp == 0) {
-    // =========================== TMA producer =================================================
+  // One thread fills a stage: the tile's key blocks, the tail and (unless aliased) the value blocks.
+  auto issue_tile = [&](int tile, int stage) {
+    mbar_expect_tx(bar_full(stage), stage_bytes);
+    const uint32_t ss = base + off_ring + stage * stage_bytes;
+    for (int kb = 0; kb < KBK; ++kb) tma_load_3d(ss + kb * BLK, &tmK, kb * 64, tile * TILE, b, bar_full(stage));
+    for (int kb = KBK; kb < KB; ++kb) tma_load_3d(ss + kb * BLK, &tmKt, (kb - KBK) * 64, tile * TILE, b, bar_full(stage));
+    if (!a.alias_v)
+      for (int vb = 0; vb < VB; ++vb) tma_load_3d(ss + (KB + vb) * BLK, &tmV, vb * 64, tile * TILE, b, bar_full(stage));
+  };
+  // A warp that is done with a stage fences its reads (generic proxy) against the refill (async
+  // proxy) and is counted; the warp that completes the count issues the TMA for the tile that reuses
+  // the stage, so no warp is set aside as a producer and nobody waits for a free stage.
+  auto release_stage_counted = [&](int tile, int stage) {
+    __syncwarp();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int tile = tile_begin; tile < tile_end; ++tile) {
-        if (!mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag)) {
-          report(a.status, XKV_ERR_TIMEOUT, 0, tile, hblk, b);
-          break;
-        }
-        mbar_expect_tx(bar_full(stage), stage_bytes);
-        const uint32_t ss = base + off_ring + stage * stage_bytes;
-        for (int kb = 0; kb < KBK; ++kb) tma_load_3d(ss + kb * BLK, &tmK, kb * 64, tile * TILE, b, bar_full(stage));
-        for (int kb = KBK; kb < KB; ++kb) tma_load_3d(ss + kb * BLK, &tmKt, (kb - KBK) * 64, tile * TILE, b, bar_full(stage));
-        if (!a.alias_v)
-          for (int vb = 0; vb < VB; ++vb) tma_load_3d(ss + (KB + vb) * BLK, &tmV, vb * 64, tile * TILE, b, bar_full(stage));
-        if (++stage == a.stages) { stage = 0; phase ^= 1u; }
+      __threadfence_block();
+      if (atomicAdd(cnt_s + stage, 1) == NCW - 1) {
+        *reinterpret_cast<volatile int*>(cnt_s + stage) = 0;
+        __threadfence_block();
+        if (tile + a.stages < tile_end) issue_tile(tile + a.stages, stage);
       }
     }
-  } else {
+  };
+  if (threadIdx.x == 0)
+    for (int i = 0; i < a.stages && tile_begin + i < tile_end; ++i) issue_tile(tile_begin + i, i);
+  {
     // =========================== compute warps ================================================
     float* wmax_s = reinterpret_cast<float*>(sm + off_wmax);
     int stage = 0;
@@ -250,9 +257,7 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                   TypeTraits<T>::from_f(sc[u][i] * a.lo_scale);
           }
         }
-        __syncwarp();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (lane == 0) mbar_arrive(bar_empty(stage));
+        release_stage_counted(tile, stage);
         if (++stage == a.stages) { stage = 0; phase ^= 1u; }
         if (*abort_flag) break;
         continue;
@@ -342,10 +347,7 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
           }
         }
       }
-      // release the stage: generic-proxy reads above, async-proxy refill next
-      __syncwarp();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      if (lane == 0) mbar_arrive(bar_empty(stage));
+      release_stage_counted(tile, stage);
       if (++stage == a.stages) { stage = 0; phase ^= 1u; }
     }
     // ---- row sums: this thread's partial for rows (mt_w, g) and (mt_w, g + 8) ------------------------
@@ -366,7 +368,7 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     return;
   }
-  if (warp >= 1 && a.logits_out == nullptr) {
+  if (a.logits_out == nullptr) {
     const float* lpart_s = reinterpret_cast<const float*>(sm + off_wmax);
     const int H = a.num_heads;
     const int nvt = a.rv / 64;
