@@ -106,6 +106,9 @@ typedef struct xkv_decode_params {
   const void* v_proj; int64_t vp_sb, vp_sh, vp_sr, vp_sd;
   void* out;          int64_t o_sb, o_sh;
   void* logits;       int64_t lg_sb, lg_sh;
+  const int32_t* kv_lens; /* device, `batch` entries, or NULL: row b attends to its first
+                             min(kv_lens[b], kv_len) cache rows (ragged batches); 0 gives a zero row.
+                             No counterpart in the reference, whose kernels take one length.       */
 } xkv_decode_params;
 
 XKV_API int xkv_version(void);

@@ -51,6 +51,7 @@ class DecodeParams(C.Structure):
         ("vp_sd", C.c_int64),
         ("out", C.c_void_p), ("o_sb", C.c_int64), ("o_sh", C.c_int64),
         ("logits", C.c_void_p), ("lg_sb", C.c_int64), ("lg_sh", C.c_int64),
+        ("kv_lens", C.c_void_p),
     ]
 
 

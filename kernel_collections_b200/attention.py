@@ -6,7 +6,9 @@ are accepted for signature compatibility; anything but None / 0.0 raises
 NotImplementedError (there is no CPU or eager fallback).
 
 Keyword-only extras, defaulting to the reference's behaviour: `sm_scale` (multiplies the
-logits), `theta`, `k_position_offset` (RoPE position of key row 0).
+logits), `theta`, `k_position_offset` (RoPE position of key row 0), `kv_lens` (int32 (bsz,)
+device tensor: row b attends to its first kv_lens[b] cache rows only — ragged batches; the
+reference's kernels take one length for the whole batch).
 """
 from __future__ import annotations
 
@@ -28,7 +30,7 @@ def _q3(query):
     return query[:, :, 0, :]
 
 
-def group_query_attention(query, key, value, attn_mask=None, dropout_p=0.0, *, sm_scale=None):
+def group_query_attention(query, key, value, attn_mask=None, dropout_p=0.0, *, sm_scale=None, kv_lens=None):
     """Dense GQA decode.  Reference: attention.py:7-90.
 
     query (bsz, num_heads, 1, head_dim); key/value (bsz, num_kv_heads, kv_len, head_dim)
@@ -47,7 +49,7 @@ def group_query_attention(query, key, value, attn_mask=None, dropout_p=0.0, *, s
         raise AssertionError("num_heads must be multiple of num_kv_heads.")
     scale = head_dim ** -0.5 if sm_scale is None else sm_scale
     o = ops.decode(entry="xkv_dense_decode", score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE,
-                   q=_q3(query), k=key.transpose(1, 2), v=value.transpose(1, 2), sm_scale=scale)
+                   q=_q3(query), k=key.transpose(1, 2), v=value.transpose(1, 2), sm_scale=scale, kv_lens=kv_lens)
     return o.unsqueeze(2)
 
 
@@ -81,7 +83,7 @@ def group_query_attention_factorized_v_only(query, key, value_A, value_B, attn_m
 
 
 def group_query_attention_factorized(query, key_A, key_B, value_A, value_B, attn_mask=None,
-                                     dropout_p=0.0, *, sm_scale=None):
+                                     dropout_p=0.0, *, sm_scale=None, kv_lens=None):
     """K = key_A @ key_B, V = value_A @ value_B in absorbed form.  Reference: attention.py:276-357.
 
     key_A (bsz, kv_len, k_rank); key_B (bsz, num_kv_heads, k_rank, head_dim); value_A / value_B
@@ -95,7 +97,8 @@ def group_query_attention_factorized(query, key_A, key_B, value_A, value_B, attn
         raise AssertionError("num_heads must be divisible by num_kv_heads")
     scale = query.shape[-1] ** -0.5 if sm_scale is None else sm_scale
     o = ops.decode(entry="xkv_absorbed_decode", score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT,
-                   q=_q3(query), k=key_A, k_proj=key_B, v=value_A, v_proj=value_B, sm_scale=scale)
+                   q=_q3(query), k=key_A, k_proj=key_B, v=value_A, v_proj=value_B, sm_scale=scale,
+                   kv_lens=kv_lens)
     return o.unsqueeze(2)
 
 
@@ -118,7 +121,7 @@ def group_query_attention_factorized_RoPE(query, key_A, key_B, value_A, value_B,
 
 # ---- entry points the reference does not have but its benchmark configurations need -------------
 def recon_rope_decode(query, key_A, key_B, value, value_B=None, *, theta, sm_scale=None,
-                      k_position_offset=0, num_splits=0, force_generic=False):
+                      k_position_offset=0, num_splits=0, force_generic=False, kv_lens=None):
     """Factorized K + RoPE with dense V (bsz, num_kv_heads, kv_len, head_dim), or factorized V
     when value_B is given (then `value` is the value latent).  key_B may be (bsz|1, num_kv_heads,
     k_rank, head_dim) or a shared (k_rank, num_kv_heads*head_dim) matrix.  Default scale
@@ -128,7 +131,7 @@ def recon_rope_decode(query, key_A, key_B, value, value_B=None, *, theta, sm_sca
     key_B = as_key_proj(key_B, D)
     scale = D ** -0.5 if sm_scale is None else sm_scale
     kw = dict(score_mode=_C.SCORE_RECON_ROPE, q=q, k=key_A, k_proj=key_B, sm_scale=scale, theta=theta,
-              pos_offset=k_position_offset, num_splits=num_splits, force_generic=force_generic)
+              pos_offset=k_position_offset, num_splits=num_splits, force_generic=force_generic, kv_lens=kv_lens)
     if value_B is None:
         o = ops.decode(entry="xkv_recon_rope_decode", value_mode=_C.VALUE_DENSE, v=value.transpose(1, 2), **kw)
     else:
@@ -160,7 +163,7 @@ def rope_query(query, theta, position):
 
 
 def xkv_group_decode(queries, key_A, key_Bs, value, value_Bs=None, *, theta, sm_scale=None,
-                     k_position_offset=0):
+                     k_position_offset=0, kv_lens=None):
     """Cross-layer group: NL layers share key_A (and the value latent when value_Bs is given).
 
     queries: sequence of (bsz, H, 1, D); key_Bs: per-layer key projections; value: the shared
@@ -171,7 +174,7 @@ def xkv_group_decode(queries, key_A, key_Bs, value, value_Bs=None, *, theta, sm_
     layers = []
     for i, q in enumerate(queries):
         kw = dict(score_mode=_C.SCORE_RECON_ROPE, q=_q3(q), k=key_A, k_proj=as_key_proj(key_Bs[i], D),
-                  sm_scale=scale, theta=theta, pos_offset=k_position_offset)
+                  sm_scale=scale, theta=theta, pos_offset=k_position_offset, kv_lens=kv_lens)
         if value_Bs is None:
             kw.update(value_mode=_C.VALUE_DENSE, v=value[i].transpose(1, 2))
         else:
@@ -180,7 +183,7 @@ def xkv_group_decode(queries, key_A, key_Bs, value, value_Bs=None, *, theta, sm_
     return [o.unsqueeze(2) for o in ops.group_decode(layers)]
 
 
-def mla_absorbed_decode(q_nope, q_rope, c_kv, k_rope, W_uk, W_uv, sm_scale):
+def mla_absorbed_decode(q_nope, q_rope, c_kv, k_rope, W_uk, W_uv, sm_scale, *, kv_lens=None):
     """MLA absorbed decode.  q_nope (b,H,nope); q_rope (b,H,rope); c_kv (b,L,lora);
     k_rope (b,L,rope); W_uk (H,nope,lora); W_uv (H,lora,v) -> (b,H,v).  W_uk is folded into q,
     the latent is streamed once for both logits and values, W_uv is applied after the merge.
@@ -189,4 +192,4 @@ def mla_absorbed_decode(q_nope, q_rope, c_kv, k_rope, W_uk, W_uv, sm_scale):
     vp = W_uv.unsqueeze(0)                       # (1, H, lora, v)
     return ops.decode(entry="xkv_mla_decode", score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT,
                       q=q_nope, k=c_kv, k_proj=kp, v=c_kv, v_proj=vp, q_tail=q_rope, k_tail=k_rope,
-                      sm_scale=sm_scale, num_kv_heads=1)
+                      sm_scale=sm_scale, num_kv_heads=1, kv_lens=kv_lens)

@@ -42,6 +42,7 @@ struct Args {
   float* logits;             // logits-only mode: fp32 sm_scale * q.k at [b * lg_sb + h * lg_sh + token]
   int64_t lg_sb, lg_sh;
   float sm_scale;
+  const int32_t* kv_lens;    // per-row lengths (ragged batches) or NULL
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, __nv_bfloat16) {
@@ -69,8 +70,10 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   uint8_t* sm = smem_raw + (base - raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int tile_begin = (int)(((int64_t)split * a.tiles_per_row) / a.num_splits);
-  const int tile_end = (int)(((int64_t)(split + 1) * a.tiles_per_row) / a.num_splits);
+  const int row_len = a.kv_lens ? min(max(a.kv_lens[b], 0), a.kv_len) : a.kv_len;   // this row's length
+  const int row_tiles = a.kv_lens ? (row_len + TILE - 1) / TILE : a.tiles_per_row;
+  const int tile_begin = (int)(((int64_t)split * row_tiles) / a.num_splits);
+  const int tile_end = (int)(((int64_t)(split + 1) * row_tiles) / a.num_splits);
   const uint32_t bar0 = base + OFF_BAR;
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
   auto bar_empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
@@ -174,7 +177,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
                 const int tok = tok0 + n * 8 + e;
-                if (tok < a.kv_len) lg[tok] = sc[n][rr * 2 + e] * a.sm_scale;
+                if (tok < row_len) lg[tok] = sc[n][rr * 2 + e] * a.sm_scale;
               }
           }
         }
@@ -195,7 +198,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int tok = tok0 + n * 8 + e;
-            v[n * 2 + e] = tok < a.kv_len ? sc[n][rr * 2 + e] * a.scale_log2 : -CUDART_INF_F;
+            v[n * 2 + e] = tok < row_len ? sc[n][rr * 2 + e] * a.scale_log2 : -CUDART_INF_F;
           }
         float mx = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -385,6 +388,7 @@ int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& pl, void* ws,
   a.lse = reinterpret_cast<float*>(w + pl.off_lse);
   a.status = status;
   a.logits = nullptr; a.lg_sb = a.lg_sh = 0; a.sm_scale = p.sm_scale;
+  a.kv_lens = p.kv_lens;
   if (sink) {
     a.logits = sink->ptr; a.lg_sb = sink->sb; a.lg_sh = sink->sh;
     return p.dtype == XKV_BF16 ? launch<__nv_bfloat16, true>(tK, tV, a, st) : launch<__half, true>(tK, tV, a, st);

@@ -103,7 +103,8 @@ decode_partial_kernel(const xkv_decode_params p, const PartialGeom g, const floa
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, b = blockIdx.y, h0 = blockIdx.z * HC;
-  const int H = p.num_heads, L = p.kv_len;
+  const int H = p.num_heads;
+  const int L = p.kv_lens ? min(max(p.kv_lens[b], 0), p.kv_len) : p.kv_len;   // this row's length
   const int G = H / p.num_kv_heads;
   const int kvh = h0 / G;
   const int tok_begin = split * g.split_len;

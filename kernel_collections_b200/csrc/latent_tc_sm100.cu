@@ -37,6 +37,7 @@ struct Args {
   float* partial_o;                     // [batch][H][splits][rv]
   float* lse;                           // [batch][H][splits]
   int* status;
+  const int32_t* kv_lens;               // per-row lengths (ragged batches) or NULL
 };
 
 __device__ __forceinline__ uint32_t swz(int row, int col_bytes) {
@@ -100,8 +101,10 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, hblk = blockIdx.y, b = blockIdx.z;
   const int h0 = hblk * HB;
-  const int tile_begin = (int)(((int64_t)split * a.tiles_per_row) / a.num_splits);
-  const int tile_end = (int)(((int64_t)(split + 1) * a.tiles_per_row) / a.num_splits);
+  const int row_len = a.kv_lens ? min(max(a.kv_lens[b], 0), a.kv_len) : a.kv_len;   // this row's length
+  const int row_tiles = a.kv_lens ? (row_len + TILE - 1) / TILE : a.tiles_per_row;
+  const int tile_begin = (int)(((int64_t)split * row_tiles) / a.num_splits);
+  const int tile_end = (int)(((int64_t)(split + 1) * row_tiles) / a.num_splits);
   const int KB = FL ? 0 : a.dk / 64, KBK = FL ? 0 : a.rk / 64, VB = a.rv / 64;
   const int vblk0 = a.alias_v ? 0 : KB;             // first 64-column block of the value rows in a stage
   const int stage_blocks = a.alias_v ? KB : KB + VB;
@@ -196,7 +199,7 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         for (int i = 0; i < 4; ++i) {
           const int h = h0 + mt_w * 16 + g + (i >> 1) * 8;
           const int tk = tok + (i & 1);
-          lgn[u][i] = (tile < tile_end && h < a.num_heads && tk < a.kv_len)
+          lgn[u][i] = (tile < tile_end && h < a.num_heads && tk < row_len)
                           ? __ldg(a.logits + (int64_t)b * a.lg_sb + (int64_t)h * a.lg_sh + tk)
                           : 0.f;
         }
@@ -252,7 +255,7 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int h = h0 + mt_w * 16 + g + (i >> 1) * 8, tk = tok + (i & 1);
-            if (h < a.num_heads && tk < a.kv_len)
+            if (h < a.num_heads && tk < row_len)
               static_cast<T*>(a.logits_out)[(int64_t)b * a.lo_sb + (int64_t)h * a.lo_sh + tk] =
                   TypeTraits<T>::from_f(sc[u][i] * a.lo_scale);
           }
@@ -270,7 +273,7 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         const int tok = tile * TILE + j * 8 + 2 * t;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          sv[u][i] = (tok + (i & 1)) < a.kv_len ? sc[u][i] * a.scale_log2 : -CUDART_INF_F;
+          sv[u][i] = (tok + (i & 1)) < row_len ? sc[u][i] * a.scale_log2 : -CUDART_INF_F;
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
           float mx = fmaxf(sv[u][rr * 2], sv[u][rr * 2 + 1]);
@@ -583,6 +586,7 @@ int latent_tc_decode(const xkv_decode_params& pin, const LatentTcPlan& pl, void*
   a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
   a.lse = reinterpret_cast<float*>(w + pl.off_lse);
   a.status = status;
+  a.kv_lens = p.kv_lens;
   const int hblocks = ceil_div(p.num_heads, pl.heads_per_cta);
   const int nt = p.v_rank / 64;
   a.logits = nullptr; a.lg_sb = a.lg_sh = 0;
@@ -656,6 +660,7 @@ int latent_pv_run(const xkv_decode_params& p, int heads, const LatentTcPlan& pl,
   a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
   a.lse = reinterpret_cast<float*>(w + pl.off_lse);
   a.status = status;
+  a.kv_lens = p.kv_lens;
   const int hblocks = ceil_div(heads, pl.heads_per_cta);
   const int nt = p.v_rank / 64;
   return p.dtype == XKV_BF16

@@ -84,6 +84,7 @@ struct Args {
   int logits_f32;                   // logits are fp32 (the first pass of a two-pass decode) instead of T
   int* status;
   int b_batched;
+  const int32_t* kv_lens;   // per-row lengths (ragged batches) or NULL
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -254,8 +255,10 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
   // tiles [range_begin, range_end) belong to this split; a pair interleaves them (leader even, peer
   // odd positions) and both CTAs run the same number of iterations, the peer possibly ending on
   // a phantom tile whose tokens are all masked
-  const int range_begin = (int)(((int64_t)split * a.tiles_per_row) / a.num_splits);
-  const int range_end = (int)(((int64_t)(split + 1) * a.tiles_per_row) / a.num_splits);
+  const int row_len = a.kv_lens ? min(max(a.kv_lens[b], 0), a.kv_len) : a.kv_len;   // this row's length
+  const int row_tiles = a.kv_lens ? (row_len + TILE_M - 1) / TILE_M : a.tiles_per_row;
+  const int range_begin = (int)(((int64_t)split * row_tiles) / a.num_splits);
+  const int range_end = (int)(((int64_t)(split + 1) * row_tiles) / a.num_splits);
   constexpr int TSTEP = PAIR ? 2 : 1;
   const int tile_begin = range_begin + (int)rank;
   const int tile_end = PAIR ? tile_begin + 2 * ((range_end - range_begin + 1) / 2) : range_end;
@@ -451,7 +454,7 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
     q_fetch(0);
     for (int tile = tile_begin; tile < tile_end; tile += TSTEP) {
       const int tok = tile * TILE_M + et;
-      const bool valid = tok < a.kv_len && tile < range_end;   // (a pair's peer may end on a phantom tile)
+      const bool valid = tok < row_len && tile < range_end;   // (a pair's peer may end on a phantom tile)
       const float pos_f = (float)(a.pos_offset + tok);
       for (int c = 0; c < NCH; ++c) {
         // ---- stage this chunk's queries: q_s[hh][j][g][{j, j+64}] = q * scale -----------------
@@ -665,7 +668,16 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
           if (pbuf == 0) pph ^= 1u;
         }
       }
-      if (alive && tile_end > tile_begin) {
+      if (alive && range_end <= range_begin) {
+        // a split without tokens (short row of a ragged batch): publish an empty partial
+        const int H = KVH * G;
+        for (int h = lane; h < H; h += 32) {
+          if (pw == 0) a.lse[(row * H + h) * out_splits + out_split] = -CUDART_INF_F;
+          float* po = a.partial_o + ((row * H + h) * out_splits + out_split) * D + pw * 32;
+          for (int d = 0; d < 32; ++d) po[d] = 0.f;
+        }
+      }
+      if (alive && range_end > range_begin) {
         // normalised partial output and log-sum-exp of this split
         const int H = KVH * G;
 #pragma unroll
@@ -844,7 +856,7 @@ bool recon_tc_group_supported(const xkv_decode_params* layers, int n) {
     if (!recon_tc_supported(b) || (b.flags & (XKV_FLAG_LOGITS_ONLY | XKV_FLAG_FORCE_GENERIC))) return false;
     if (a.q_sb != b.q_sb || a.q_sh != b.q_sh || a.sm_scale != b.sm_scale || a.theta != b.theta ||
         a.pos_offset != b.pos_offset || a.inv_freq != b.inv_freq || a.k != b.k || a.k_sb != b.k_sb ||
-        a.k_sl != b.k_sl || (a.kp_sb != 0) != (b.kp_sb != 0))
+        a.k_sl != b.k_sl || (a.kp_sb != 0) != (b.kp_sb != 0) || a.kv_lens != b.kv_lens)
       return false;
   }
   return true;
@@ -921,6 +933,7 @@ int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcP
   }
   a.status = status;
   a.b_batched = b_batched;
+  a.kv_lens = p.kv_lens;
 
   int rc;
 #define XKV_TC(T, GG) rc = lo ? launch<T, GG, true>(maps, a, pl.pair != 0, st) : launch<T, GG, false>(maps, a, pl.pair != 0, st)
@@ -956,7 +969,7 @@ bool recon_tc_logits_supported(const xkv_decode_params* layers, int n) {
     const xkv_decode_params &a = layers[0], &b = layers[i];
     if (a.q_sb != b.q_sb || a.q_sh != b.q_sh || a.sm_scale != b.sm_scale || a.theta != b.theta ||
         a.pos_offset != b.pos_offset || a.inv_freq != b.inv_freq || a.k != b.k || a.k_sb != b.k_sb ||
-        a.k_sl != b.k_sl || (a.kp_sb != 0) != (b.kp_sb != 0))
+        a.k_sl != b.k_sl || (a.kp_sb != 0) != (b.kp_sb != 0) || a.kv_lens != b.kv_lens)
       return false;
   }
   return true;

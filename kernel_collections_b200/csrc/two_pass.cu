@@ -17,7 +17,8 @@ namespace xkv {
 namespace {
 bool same_values(const xkv_decode_params& a, const xkv_decode_params& b) {
   return a.v == b.v && a.v_sb == b.v_sb && a.v_sl == b.v_sl && a.v_rank == b.v_rank && a.value_dim == b.value_dim &&
-         a.batch == b.batch && a.kv_len == b.kv_len && a.num_heads == b.num_heads && a.dtype == b.dtype;
+         a.batch == b.batch && a.kv_len == b.kv_len && a.num_heads == b.num_heads && a.dtype == b.dtype &&
+         a.kv_lens == b.kv_lens;
 }
 }  // namespace
 

@@ -47,6 +47,7 @@ def build_params(
     force_generic: bool = False,
     num_kv_heads: Optional[int] = None,
     rope_table: Optional[torch.Tensor] = None,   # (L, D/2, 2) fp32 {cos, sin}
+    kv_lens: Optional[torch.Tensor] = None,      # (b,) int32: per-row cache lengths (ragged batches)
 ):
     """Validate shapes and fill one xkv_decode_params block.  Returns (params, result tensor)."""
     _C.require_cuda(q, k, v, k_proj, v_proj, q_tail, k_tail, out)
@@ -150,6 +151,13 @@ def build_params(
             f = _C.inv_freq(D, theta, dev)
             keep.append(f)
             p.inv_freq = f.data_ptr()
+
+    if kv_lens is not None:
+        _C.require_cuda(kv_lens)
+        if kv_lens.dtype != torch.int32 or tuple(kv_lens.shape) != (b,) or not kv_lens.is_contiguous():
+            raise ValueError("kv_lens must be a contiguous int32 tensor of shape (batch,)")
+        keep.append(kv_lens)
+        p.kv_lens = kv_lens.data_ptr()
 
     result = None
     if logits_only:
