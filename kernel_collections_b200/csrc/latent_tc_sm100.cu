@@ -117,8 +117,7 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
   const uint32_t off_ring = (q_bytes + 1023u) & ~1023u;
   const uint32_t off_p = off_ring + a.stages * stage_bytes;     // [HB][32 tokens] bf16, 64 B rows
   const uint32_t off_wmax = off_p + HB * 64;                    // [HB][4] floats (per 8-token group)
-  const uint32_t off_l = off_wmax + HB * 16;                    // [HB] floats
-  const uint32_t off_bar = off_l + HB * 4;
+  const uint32_t off_bar = off_wmax + HB * 16;
   auto bar_full = [&](int s) { return base + off_bar + 8u * s; };
   int* cnt_s = reinterpret_cast<int*>(sm + off_bar + 32);      // per stage: warps that finished reading it
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + off_bar + 64);
@@ -454,7 +453,7 @@ size_t smem_need(const xkv_decode_params& p, int hb, int stages) {
   const bool alias = p.v == p.k && p.v_sl == p.k_sl && p.v_sb == p.k_sb && p.v_rank <= p.k_rank;
   const size_t q = align_up((size_t)(dk / 64) * hb * 128, 1024);
   const size_t stage = (size_t)((dk / 64) + (alias ? 0 : p.v_rank / 64)) * TILE * 128;
-  return q + stages * stage + hb * 64 + hb * 16 + hb * 4 + 64 + 16;
+  return q + stages * stage + hb * 64 + hb * 16 + 64 + 16;
 }
 
 template <typename T, int HB, int NT, bool FL>
@@ -615,7 +614,7 @@ bool latent_pv_supported(const xkv_decode_params& p) {
 bool latent_pv_plan(const xkv_decode_params& p, int heads, LatentTcPlan* pl) {
   const int hb = (heads > 32 && p.v_rank <= 512) ? 64 : 32;
   const size_t stage = (size_t)(p.v_rank / 64) * TILE * 128;
-  auto need = [&](int stages) { return stages * stage + hb * 64 + hb * 16 + hb * 4 + 64 + 16; };
+  auto need = [&](int stages) { return stages * stage + hb * 64 + hb * 16 + 64 + 16; };
   int stages = 4;
   while (stages > 2 && need(stages) > (size_t)MAX_SMEM) --stages;
   pl->heads_per_cta = hb;

@@ -836,7 +836,6 @@ static bool plan_layers(const xkv_decode_params& p, int num_layers, ReconTcPlan*
   pl->tiles_per_split = tiles;   // tiles per batch row; the kernel cuts [s*T/S, (s+1)*T/S)
   const int out_splits = pl->num_splits * (pl->pair ? 2 : 1);
   size_t off = 256;              // status words
-  pl->off_table = off;
   pl->off_partial = off;
   const bool lo = (p.flags & XKV_FLAG_LOGITS_ONLY) != 0;
   const size_t nrows = (size_t)num_layers * p.batch * p.num_heads * out_splits;

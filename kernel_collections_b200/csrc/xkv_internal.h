@@ -43,7 +43,7 @@ struct ReconTcPlan {
   int pair;             // CTA pairs (cta_group::2) instead of single CTAs
   int num_splits;       // CTAs (or CTA pairs) per batch row
   int tiles_per_split;  // 128-token tiles per CTA
-  size_t off_table, off_partial, off_lse, total_bytes;
+  size_t off_partial, off_lse, total_bytes;
 };
 bool recon_tc_supported(const xkv_decode_params& p);
 bool recon_tc_plan(const xkv_decode_params& p, ReconTcPlan* plan);

@@ -87,3 +87,46 @@ def test_cpu_tensors_are_rejected_loudly():
         K.group_query_attention(q, kv, kv, attn_mask=torch.zeros(1, 1, 1, 8))
     with pytest.raises(NotImplementedError):
         K.group_query_attention(q, kv, kv, dropout_p=0.1)
+
+
+def _blk(**kw):
+    p = _C.DecodeParams()
+    p.dtype = _C.XKV_BF16
+    p.batch, p.num_heads, p.num_kv_heads, p.kv_len = 4, 32, 8, 4096
+    p.head_dim = p.value_dim = 128
+    p.sm_scale = 1.0
+    p.q = p.k = p.v = p.out = 0x10000          # aligned dummies, never dereferenced on the host
+    p.q_sb, p.q_sh = 32 * 128, 128
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+def test_kernel_selection_is_host_side_and_follows_the_shape():
+    """xkv_decode_plan launches nothing: which kernel family serves which call."""
+    lib = _C.load()
+    plan = lambda p: lib.xkv_decode_plan(C.byref(p))
+    dense = dict(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, k_sb=4096 * 1024, k_sl=1024, k_sh=128,
+                 v_sb=4096 * 1024, v_sl=1024, v_sh=128)
+    assert plan(_blk(**dense)) == b"dense_tc"
+    assert plan(_blk(**dense, dtype=_C.XKV_F32)) == b"generic"
+    assert plan(_blk(**dense, flags=_C.FLAG_FORCE_GENERIC)) == b"generic"
+    assert plan(_blk(**dense, k=0x10002)) == b"generic"                      # unaligned cache pointer
+    recon = dict(score_mode=_C.SCORE_RECON_ROPE, k_rank=512, k_sb=4096 * 512, k_sl=512, k_proj=0x20000, k_proj_heads=8,
+                 kp_sb=0, kp_sh=128, kp_sr=1024, kp_sd=1, theta=5e5)
+    vdense = dict(value_mode=_C.VALUE_DENSE, v_sb=4096 * 1024, v_sl=1024, v_sh=128)
+    assert plan(_blk(**recon, **vdense)) == b"recon_tc"
+    assert plan(_blk(**{**recon, "k_rank": 500, "k_sl": 500, "k_sb": 4096 * 500}, **vdense)) == b"generic"
+    vlat = dict(value_mode=_C.VALUE_LATENT, v_rank=512, v_sb=4096 * 512, v_sl=512, v_proj=0x30000, v_proj_heads=8,
+                vp_sb=0, vp_sh=128, vp_sr=1024, vp_sd=1)
+    assert plan(_blk(**recon, **vlat)) == b"two_pass"
+    assert plan(_blk(**dense | vlat)) == b"two_pass"
+    lat = dict(score_mode=_C.SCORE_LATENT, k_rank=256, k_sb=4096 * 256, k_sl=256, k_proj=0x20000, k_proj_heads=8,
+               kp_sb=0, kp_sh=256 * 128, kp_sr=128, kp_sd=1)
+    assert plan(_blk(**lat, **vlat)) == b"latent_tc"
+    assert plan(_blk(**lat, **{**vlat, "v_rank": 100, "v_sl": 100})) == b"generic"
+    # packed MLA cache: one KV head, 576-wide keys, values = their 512-wide prefix
+    packed = dict(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, num_kv_heads=1, head_dim=576, value_dim=512,
+                  k_sb=4096 * 576, k_sl=576, k_sh=576, v_sb=4096 * 576, v_sl=576, v_sh=576, q_sb=32 * 576, q_sh=576)
+    assert plan(_blk(**packed)) == b"latent_tc"
+    assert plan(_blk(**packed, logit_cap=5.0)) == b"generic"
