@@ -109,6 +109,11 @@ typedef struct xkv_decode_params {
   const int32_t* kv_lens; /* device, `batch` entries, or NULL: row b attends to its first
                              min(kv_lens[b], kv_len) cache rows (ragged batches); 0 gives a zero row.
                              No counterpart in the reference, whose kernels take one length.       */
+  float* lse_out;     int64_t lse_sb; /* optional (batch, H) fp32 at [b * lse_sb + h]: natural-log
+                             sum-exp of the scaled logits of each head (-inf for an empty row).  With it the
+                             results of calls over disjoint parts of a cache can be merged exactly
+                             (xkv_merge), e.g. a factorized prefill cache plus a dense tail of fresh tokens:
+                             flash_decoding/deepseek_mla/flash_decoding.py:66-255 in the reference.  NULL = off. */
 } xkv_decode_params;
 
 XKV_API int xkv_version(void);

@@ -52,6 +52,7 @@ class DecodeParams(C.Structure):
         ("out", C.c_void_p), ("o_sb", C.c_int64), ("o_sh", C.c_int64),
         ("logits", C.c_void_p), ("lg_sb", C.c_int64), ("lg_sh", C.c_int64),
         ("kv_lens", C.c_void_p),
+        ("lse_out", C.c_void_p), ("lse_sb", C.c_int64),
     ]
 
 

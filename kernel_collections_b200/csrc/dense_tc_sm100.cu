@@ -396,7 +396,7 @@ int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& pl, void* ws,
   const int rc = p.dtype == XKV_BF16 ? launch<__nv_bfloat16, false>(tK, tV, a, st) : launch<__half, false>(tK, tV, a, st);
   if (rc != XKV_OK) return rc;
   return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, D, D, nullptr, 1, 0, 0,
-                      0, 0, p.o_sb, p.o_sh, st);
+                      0, 0, p.o_sb, p.o_sh, st, 0, 0, p.lse_out, p.lse_sb);
 }
 
 }  // namespace xkv

@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(NT)
 merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ lse, T* __restrict__ out,
              int num_heads, int heads_total, int head_offset, int S, int Dacc, int Dv, const T* __restrict__ v_proj, int v_div,
              int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd, int64_t o_sb, int64_t o_sh,
-             int vec_proj) {
+             int vec_proj, float* __restrict__ lse_out, int64_t lse_sb) {
   extern __shared__ float smem[];
   float* w_s = smem;          // [S]
   float* o_s = smem + S;      // [Dacc]
@@ -331,6 +331,8 @@ merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ lse,
     float tot = 0.f;
     for (int s = 0; s < S; ++s) tot += w_s[s];  // fixed order
     bcast[1] = tot > 0.f ? 1.f / tot : 0.f;
+    // log-sum-exp over the whole row, for callers that merge several calls
+    if (lse_out) lse_out[(int64_t)b * lse_sb + h] = tot > 0.f ? mx + logf(tot) : -CUDART_INF_F;
   }
   __syncthreads();
   const float inv = bcast[1];
@@ -416,7 +418,7 @@ int run_generic(const xkv_decode_params& p, const GenericPlan& pl, void* ws, cud
   if (!(p.flags & XKV_FLAG_LOGITS_ONLY)) {
     int rc = launch_merge(partial, lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, pl.acc_dim,
                           p.value_dim, p.value_mode == XKV_VALUE_LATENT ? p.v_proj : nullptr,
-                          p.v_proj_heads, p.vp_sb, p.vp_sh, p.vp_sr, p.vp_sd, p.o_sb, p.o_sh, st);
+                          p.v_proj_heads, p.vp_sb, p.vp_sh, p.vp_sr, p.vp_sd, p.o_sb, p.o_sh, st, 0, 0, p.lse_out, p.lse_sb);
     if (rc != XKV_OK) return rc;
   }
   return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
@@ -525,7 +527,7 @@ int generic_decode_builtin_scratch(const xkv_decode_params& p, const GenericPlan
 int launch_merge(const float* partial_o, const float* lse, void* out, int dtype, int batch, int num_heads,
                  int num_splits, int acc_dim, int value_dim, const void* v_proj, int v_proj_heads,
                  int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd, int64_t o_sb, int64_t o_sh,
-                 cudaStream_t st, int heads_total, int head_offset) {
+                 cudaStream_t st, int heads_total, int head_offset, float* lse_out, int64_t lse_sb) {
   if (heads_total <= 0) heads_total = num_heads;
   const size_t smem = (size_t)(num_splits + acc_dim) * sizeof(float);
   if (smem > 40 * 1024) return XKV_ERR_UNSUPPORTED;
@@ -542,7 +544,7 @@ int launch_merge(const float* partial_o, const float* lse, void* out, int dtype,
   merge_kernel<T><<<grid, NT, smem, st>>>(partial_o, lse, static_cast<T*>(out), num_heads, heads_total, \
                                           head_offset, num_splits,                                  \
                                           acc_dim, value_dim, static_cast<const T*>(v_proj), div, vp_sb, \
-                                          vp_sh, vp_sr, vp_sd, o_sb, o_sh, vec_proj)
+                                          vp_sh, vp_sr, vp_sd, o_sb, o_sh, vec_proj, lse_out, lse_sb)
   switch (dtype) {
     case XKV_F32: XKV_MERGE(float); break;
     case XKV_BF16: XKV_MERGE(__nv_bfloat16); break;

@@ -595,7 +595,8 @@ int latent_tc_decode(const xkv_decode_params& pin, const LatentTcPlan& pl, void*
                      : dispatch<__half, false>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st);
   if (rc != XKV_OK || lo) return rc;
   return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, p.v_rank, p.value_dim,
-                      p.v_proj, p.v_proj ? p.v_proj_heads : 1, p.vp_sb, p.vp_sh, p.vp_sr, p.vp_sd, p.o_sb, p.o_sh, st);
+                      p.v_proj, p.v_proj ? p.v_proj_heads : 1, p.vp_sb, p.vp_sh, p.vp_sr, p.vp_sd, p.o_sb, p.o_sh, st, 0, 0,
+                      p.lse_out, p.lse_sb);
 }
 
 // ---- second pass of the two-pass decode: softmax(logits) . A_v over `heads` stacked heads ----------

@@ -948,7 +948,8 @@ int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcP
   const size_t layer_rows = (size_t)p.batch * p.num_heads * out_splits;
   for (int i = 0; i < n; ++i) {
     rc = launch_merge(a.partial_o + i * layer_rows * D, a.lse + i * layer_rows, layers[i].out, p.dtype, p.batch,
-                      p.num_heads, out_splits, D, D, nullptr, 1, 0, 0, 0, 0, layers[i].o_sb, layers[i].o_sh, st);
+                      p.num_heads, out_splits, D, D, nullptr, 1, 0, 0, 0, 0, layers[i].o_sb, layers[i].o_sh, st, 0, 0, layers[i].lse_out,
+                      layers[i].lse_sb);
     if (rc != XKV_OK) return rc;
   }
   return XKV_OK;

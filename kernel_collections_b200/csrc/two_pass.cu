@@ -95,7 +95,7 @@ int two_pass_decode(const xkv_decode_params* layers, int n, const TwoPassPlan& p
     const xkv_decode_params& li = layers[i];
     rc = launch_merge(partial, lse, li.out, p.dtype, p.batch, H, pl.pv.num_splits, p.v_rank, li.value_dim, li.v_proj,
                       li.v_proj ? li.v_proj_heads : 1, li.vp_sb, li.vp_sh, li.vp_sr, li.vp_sd, li.o_sb, li.o_sh, st,
-                      heads, i * H);
+                      heads, i * H, li.lse_out, li.lse_sb);
     if (rc != XKV_OK) return rc;
   }
   return XKV_OK;

@@ -34,7 +34,8 @@ int generic_decode_builtin_scratch(const xkv_decode_params& p, const GenericPlan
 int launch_merge(const float* partial_o, const float* lse, void* out, int dtype, int batch,
                  int num_heads, int num_splits, int acc_dim, int value_dim, const void* v_proj,
                  int v_proj_heads, int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd,
-                 int64_t o_sb, int64_t o_sh, cudaStream_t st, int heads_total = 0, int head_offset = 0);
+                 int64_t o_sb, int64_t o_sh, cudaStream_t st, int heads_total = 0, int head_offset = 0,
+                 float* lse_out = nullptr, int64_t lse_sb = 0);
 int launch_rope_table(float* cos_sin, int kv_len, int half, int pos_offset, float theta,
                       const float* inv_freq, cudaStream_t st);
 

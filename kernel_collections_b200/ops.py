@@ -48,6 +48,7 @@ def build_params(
     num_kv_heads: Optional[int] = None,
     rope_table: Optional[torch.Tensor] = None,   # (L, D/2, 2) fp32 {cos, sin}
     kv_lens: Optional[torch.Tensor] = None,      # (b,) int32: per-row cache lengths (ragged batches)
+    return_lse: bool = False,                    # also return the (b, H) fp32 log-sum-exp of the scaled logits
 ):
     """Validate shapes and fill one xkv_decode_params block.  Returns (params, result tensor)."""
     _C.require_cuda(q, k, v, k_proj, v_proj, q_tail, k_tail, out)
@@ -170,6 +171,13 @@ def build_params(
             raise ValueError(f"output must be a ({b}, {H}, {p.value_dim}) {q.dtype} tensor with a contiguous last dim")
         p.out, p.o_sb, p.o_sh = out.data_ptr(), _stride(out, 0), _stride(out, 1)
         result = out
+    if return_lse:
+        if logits_only:
+            raise ValueError("return_lse needs a softmax: not available with logits_only")
+        lse = torch.empty((b, H), dtype=torch.float32, device=dev)
+        keep.append(lse)
+        p.lse_out, p.lse_sb = lse.data_ptr(), lse.stride(0)
+        result = (result, lse)
     p._keepalive = (q, k, v, k_proj, v_proj, q_tail, k_tail, keep)   # contiguous copies made above
     return p, result
 
@@ -189,6 +197,22 @@ def decode_builtin_scratch(**kw):
     p, result = build_params(**kw)
     _C.run_decode_builtin_scratch(p, kw["q"].device)
     return result
+
+
+def merge_segments(outs, lses):
+    """Exact merge of decode results over disjoint parts of a cache (e.g. a factorized prefill cache
+    and a dense tail): outs[i] (b, H, dim) with lses[i] (b, H) from decode(..., return_lse=True).
+    Runs the library's split-merge kernel (xkv_merge); empty parts (lse = -inf) drop out."""
+    o0 = outs[0]
+    b, H, dim = o0.shape
+    part = torch.stack([o.float() for o in outs], dim=2).contiguous()          # (b, H, S, dim)
+    lse = torch.stack(list(lses), dim=2).contiguous()                          # (b, H, S)
+    out = torch.empty((b, H, dim), dtype=o0.dtype, device=o0.device)
+    lib = _C.load()
+    rc = lib.xkv_merge(part.data_ptr(), lse.data_ptr(), out.data_ptr(), _C.dtype_code(o0), b, H, len(outs), dim,
+                       out.stride(0), out.stride(1), torch.cuda.current_stream(o0.device).cuda_stream)
+    _C.check(rc, "xkv_merge")
+    return out
 
 
 def plan(**kw):

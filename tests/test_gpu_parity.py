@@ -298,3 +298,36 @@ def test_error_behaviour_on_gpu():
         K.group_query_attention(q.double(), kv.double(), kv.double())
     with pytest.raises(AssertionError):
         FR.qAB_rope_v1(q, torch.randn(1, 8, 5, device=DEV), torch.randn(1, 2, 6, 16, device=DEV))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prefill_decode_separated_buffers(dtype):
+    """deepseek_mla pd_sep entry points: one cache split into a prefill part and a decoded tail must
+    equal attention over the concatenated cache, including a tail that a merged-length split table
+    would have dropped."""
+    b, H, KVH, D, Lp, Ld = 2, 16, 1, 128, 1000, 37
+    gen = g(10)
+    q, qd = mk((b, H, D), dtype, 0.5, gen=gen)
+    kp, kpd = mk((b, Lp, KVH, D), dtype, gen=gen)
+    vp, vpd = mk((b, Lp, KVH, D), dtype, gen=gen)
+    kdn, kdd = mk((b, Ld, KVH, D), dtype, gen=gen)
+    vdn, vdd = mk((b, Ld, KVH, D), dtype, gen=gen)
+    got = FD.deepseek_mla.mla_decode_attention_fwd_pd_sep(qd, kpd, vpd, kdd, vdd, 0.2)
+    want = O.flash_decode_gqa(q, torch.cat([kp, kdn], 1), torch.cat([vp, vdn], 1), 0.2)
+    check(got, want, dtype, "pd_sep")
+    # factorized prefill cache
+    R = 64
+    kA, kAd = mk((b, Lp, R), dtype, gen=gen)
+    kB, kBd = mk((b, KVH, R, D), dtype, R ** -0.5, gen=gen)
+    vA, vAd = mk((b, Lp, R), dtype, gen=gen)
+    vB, vBd = mk((b, KVH, R, D), dtype, R ** -0.5, gen=gen)
+    got = FD.deepseek_mla.mla_decode_attention_fwd_pd_sep_xKV(qd, kAd, kBd, vAd, vBd, kdd, vdd, 0.2)
+    Kp = torch.matmul(kA.float().unsqueeze(1), kB.float()).transpose(1, 2)      # (b, Lp, KVH, D)
+    Vp = torch.matmul(vA.float().unsqueeze(1), vB.float()).transpose(1, 2)
+    want = O.flash_decode_gqa(q, torch.cat([Kp, kdn.float()], 1), torch.cat([Vp, vdn.float()], 1), 0.2)
+    check(got, want, dtype, "pd_sep_xKV")
+    # the log-sum-exp itself
+    o, lse = ops.decode(entry="xkv_dense_decode", score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, q=qd, k=kpd,
+                        v=vpd, sm_scale=0.2, return_lse=True)
+    s = torch.einsum("bhd,blkd->bhl", q.float(), kp.float()) * 0.2
+    assert (lse.cpu() - torch.logsumexp(s, -1)).abs().max().item() < (2e-2 if dtype != torch.float32 else 1e-4)
