@@ -114,6 +114,10 @@ typedef struct xkv_decode_params {
                              results of calls over disjoint parts of a cache can be merged exactly
                              (xkv_merge), e.g. a factorized prefill cache plus a dense tail of fresh tokens:
                              flash_decoding/deepseek_mla/flash_decoding.py:66-255 in the reference.  NULL = off. */
+  const void* mask;   int64_t mask_sb, mask_sh; /* optional additive mask of the call's dtype, added to
+                             the scaled logits before the softmax: mask[b * mask_sb + h * mask_sh + token]; strides
+                             of 0 broadcast over the batch / the heads (attention.py:60-64 in the reference).  Calls
+                             with a mask run on the portable kernels.  NULL = no mask.                        */
 } xkv_decode_params;
 
 XKV_API int xkv_version(void);

@@ -53,6 +53,7 @@ class DecodeParams(C.Structure):
         ("logits", C.c_void_p), ("lg_sb", C.c_int64), ("lg_sh", C.c_int64),
         ("kv_lens", C.c_void_p),
         ("lse_out", C.c_void_p), ("lse_sb", C.c_int64),
+        ("mask", C.c_void_p), ("mask_sb", C.c_int64), ("mask_sh", C.c_int64),
     ]
 
 

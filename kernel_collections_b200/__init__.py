@@ -8,6 +8,8 @@ eager fallback — tensors must live on a CUDA device.
 from .attention import (  # noqa: F401
     group_query_attention,
     group_query_attention_fa,
+    group_query_attention_sdpa,
+    group_query_attentionv2,
     group_query_attention_factorized,
     group_query_attention_factorized_v_only,
     group_query_attention_factorized_RoPE,

@@ -1,9 +1,11 @@
 """Drop-in equivalents of the reference's eager decode functions (attention.py there).
 
 Same names, argument order, shapes and return values; the work runs in libxkv's CUDA
-kernels.  All functions are single decode steps (q_len == 1).  `attn_mask` and `dropout_p`
-are accepted for signature compatibility; anything but None / 0.0 raises
-NotImplementedError (there is no CPU or eager fallback).
+kernels.  All functions are single decode steps (q_len == 1).  `attn_mask` is the reference's
+additive mask (added to the scaled logits before the softmax, attention.py:60-64), any shape
+that broadcasts to (bsz, num_kv_heads, group, 1, kv_len) / (bsz, num_heads, 1, kv_len); masked
+calls run on the portable kernels.  `dropout_p` other than 0.0 raises NotImplementedError
+(training-only; there is no CPU or eager fallback).
 
 Keyword-only extras, defaulting to the reference's behaviour: `sm_scale` (multiplies the
 logits), `theta`, `k_position_offset` (RoPE position of key row 0), `kv_lens` (int32 (bsz,)
@@ -19,7 +21,27 @@ from . import _C, ops
 
 def _no_mask(attn_mask, dropout_p):
     if attn_mask is not None or dropout_p != 0.0:
-        raise NotImplementedError("attn_mask / dropout are not supported by the decode kernels")
+        raise NotImplementedError("attn_mask / dropout are not supported by this entry point")
+
+
+def _mask3(attn_mask, dropout_p, bsz, num_heads, num_kv_heads, kv_len):
+    """The reference adds attn_mask to logits shaped (bsz, num_kv_heads, group, kv_len) (attention.py:63,
+    q_len == 1 folded away); return it as something that broadcasts to (bsz, num_heads, kv_len)."""
+    if dropout_p != 0.0:
+        raise NotImplementedError("dropout is training-only and not supported by the decode kernels")
+    if attn_mask is None:
+        return None
+    m = attn_mask
+    G = num_heads // num_kv_heads
+    if m.dim() == 5:                       # (bsz|1, kvh|1, G|1, 1, L)
+        m = m.expand(m.shape[0], num_kv_heads, G, 1, m.shape[-1]).reshape(m.shape[0], num_heads, m.shape[-1])
+    elif m.dim() == 4:                     # (bsz|1, heads|1, 1, L)
+        m = m[:, :, 0, :]
+    elif m.dim() == 2:                     # (q_len = 1, L)
+        m = m[None]
+    if m.dim() != 3:
+        raise ValueError(f"unsupported attn_mask shape {tuple(attn_mask.shape)}")
+    return m
 
 
 def _q3(query):
@@ -35,8 +57,8 @@ def group_query_attention(query, key, value, attn_mask=None, dropout_p=0.0, *, s
 
     query (bsz, num_heads, 1, head_dim); key/value (bsz, num_kv_heads, kv_len, head_dim)
     -> (bsz, num_heads, 1, head_dim).  Logits are divided by sqrt(head_dim) as there."""
-    _no_mask(attn_mask, dropout_p)
     bsz, num_heads, _, head_dim = query.shape
+    mask = _mask3(attn_mask, dropout_p, bsz, num_heads, key.shape[1], key.shape[2])
     if key.shape[0] != bsz or value.shape[0] != bsz:
         raise AssertionError("Batch size mismatch among Q, K, V.")
     if key.shape[1] != value.shape[1]:
@@ -49,8 +71,22 @@ def group_query_attention(query, key, value, attn_mask=None, dropout_p=0.0, *, s
         raise AssertionError("num_heads must be multiple of num_kv_heads.")
     scale = head_dim ** -0.5 if sm_scale is None else sm_scale
     o = ops.decode(entry="xkv_dense_decode", score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE,
-                   q=_q3(query), k=key.transpose(1, 2), v=value.transpose(1, 2), sm_scale=scale, kv_lens=kv_lens)
+                   q=_q3(query), k=key.transpose(1, 2), v=value.transpose(1, 2), sm_scale=scale, kv_lens=kv_lens,
+                   mask=mask)
     return o.unsqueeze(2)
+
+
+def group_query_attentionv2(query, key, value, attn_mask=None, dropout_p=0.0):
+    """The reference's second formulation of the same op (attention.py:93-182: keys / values
+    broadcast over the group axis instead of folding the group into rows).  It also accepts
+    q_len > 1 there; the decode kernels take the single-step case only."""
+    return group_query_attention(query, key, value, attn_mask, dropout_p)
+
+
+def group_query_attention_sdpa(query, key, value, attn_mask=None, dropout_p=0.0):
+    """Reference: attention.py:193-200, F.scaled_dot_product_attention(..., enable_gqa=True): the same
+    math with the default 1/sqrt(head_dim) scale and an additive float mask."""
+    return group_query_attention(query, key, value, attn_mask, dropout_p)
 
 
 def group_query_attention_fa(query, key, value, attn_mask=None, dropout_p=0.0):
@@ -71,14 +107,14 @@ def group_query_attention_factorized_v_only(query, key, value_A, value_B, attn_m
 
     key (bsz, num_kv_heads, kv_len, head_dim); value_A (bsz, kv_len, v_rank);
     value_B (bsz, num_kv_heads, v_rank, head_dim)."""
-    _no_mask(attn_mask, dropout_p)
+    mask = _mask3(attn_mask, dropout_p, query.shape[0], query.shape[1], key.shape[1], key.shape[2])
     if value_A.shape[-1] != value_B.shape[2]:
         raise AssertionError("Rank mismatch between value_A and value_B")
     if query.shape[1] % key.shape[1] != 0:
         raise AssertionError("num_heads must be divisible by num_kv_heads")
     o = ops.decode(entry="xkv_absorbed_decode", score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_LATENT,
                    q=_q3(query), k=key.transpose(1, 2), v=value_A, v_proj=value_B,
-                   sm_scale=query.shape[-1] ** -0.5)
+                   sm_scale=query.shape[-1] ** -0.5, mask=mask)
     return o.unsqueeze(2)
 
 
@@ -88,7 +124,7 @@ def group_query_attention_factorized(query, key_A, key_B, value_A, value_B, attn
 
     key_A (bsz, kv_len, k_rank); key_B (bsz, num_kv_heads, k_rank, head_dim); value_A / value_B
     alike.  Logits are divided by sqrt(head_dim)."""
-    _no_mask(attn_mask, dropout_p)
+    mask = _mask3(attn_mask, dropout_p, query.shape[0], query.shape[1], key_B.shape[1], key_A.shape[1])
     if key_A.shape[-1] != key_B.shape[2]:
         raise AssertionError("Rank mismatch between key_A and key_B")
     if value_A.shape[-1] != value_B.shape[2]:
@@ -98,7 +134,7 @@ def group_query_attention_factorized(query, key_A, key_B, value_A, value_B, attn
     scale = query.shape[-1] ** -0.5 if sm_scale is None else sm_scale
     o = ops.decode(entry="xkv_absorbed_decode", score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT,
                    q=_q3(query), k=key_A, k_proj=key_B, v=value_A, v_proj=value_B, sm_scale=scale,
-                   kv_lens=kv_lens)
+                   kv_lens=kv_lens, mask=mask)
     return o.unsqueeze(2)
 
 
@@ -108,14 +144,14 @@ def group_query_attention_factorized_RoPE(query, key_A, key_B, value_A, value_B,
     """Factorized K with RoPE applied to the rebuilt keys, factorized V.  Reference:
     attention.py:360-431 — logits q . RoPE_l(key_A[l] @ key_B) with theta 1e7 and NO 1/sqrt(d)
     scaling (:393-396), key position = row index, q used as given."""
-    _no_mask(attn_mask, dropout_p)
+    mask = _mask3(attn_mask, dropout_p, query.shape[0], query.shape[1], key_B.shape[1], key_A.shape[1])
     if key_A.shape[-1] != key_B.shape[2]:
         raise AssertionError("Rank mismatch between key_A and key_B")
     if value_A.shape[-1] != value_B.shape[2]:
         raise AssertionError("Rank mismatch between value_A and value_B")
     o = ops.decode(entry="xkv_recon_rope_decode", score_mode=_C.SCORE_RECON_ROPE,
                    value_mode=_C.VALUE_LATENT, q=_q3(query), k=key_A, k_proj=key_B, v=value_A,
-                   v_proj=value_B, sm_scale=sm_scale, theta=theta, pos_offset=k_position_offset)
+                   v_proj=value_B, sm_scale=sm_scale, theta=theta, pos_offset=k_position_offset, mask=mask)
     return o.unsqueeze(2)
 
 

@@ -323,6 +323,7 @@ static bool keys_ok(const xkv_decode_params& p) {
   if (p.score_mode != XKV_SCORE_DENSE) return false;
   if (p.dtype != XKV_BF16 && p.dtype != XKV_F16) return false;
   if (p.head_dim != D || p.tail_dim != 0 || p.logit_cap > 0.f) return false;
+  if (p.mask) return false;   // additive masks run on the portable kernels
   if (p.num_heads / p.num_kv_heads > 16) return false;
   if (!aligned16(p.k) || (reinterpret_cast<uintptr_t>(p.q) & 3u)) return false;
   if (!stride_ok(p.k_sl) || (p.num_kv_heads > 1 && !stride_ok(p.k_sh)) || (p.batch > 1 && !stride_ok(p.k_sb))) return false;

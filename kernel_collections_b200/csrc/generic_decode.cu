@@ -208,6 +208,8 @@ decode_partial_kernel(const xkv_decode_params p, const PartialGeom g, const floa
         if (h < HC) {
           float s = warp_sum(part[h]) * p.sm_scale;
           if (p.logit_cap > 0.f) s = p.logit_cap * tanhf(s / p.logit_cap);
+          if (p.mask && tok < tok_end)
+            s += ldf(static_cast<const T*>(p.mask) + (int64_t)b * p.mask_sb + (int64_t)(h0 + h) * p.mask_sh + tok);
           if (lane == 0) {
             if (logits_only) {
               if (tok < tok_end)

@@ -503,6 +503,7 @@ bool latent_tc_supported(const xkv_decode_params& pin) {
   const xkv_decode_params p = normalized(pin);
   if (p.dtype != XKV_BF16 && p.dtype != XKV_F16) return false;
   if (p.logit_cap > 0.f) return false;
+  if (p.mask) return false;   // additive masks run on the portable kernels
   if (p.k_rank % 64 != 0 || p.v_rank % 128 != 0 || p.tail_dim % 64 != 0) return false;
   if (p.v_rank > 1024 || p.k_rank + p.tail_dim > 1152) return false;
   if (!aligned16(p.k) || !aligned16(p.v) || !stride_ok(p.k_sl) || !stride_ok(p.v_sl)) return false;
@@ -608,6 +609,7 @@ bool latent_pv_supported(const xkv_decode_params& p) {
   if (p.value_mode != XKV_VALUE_LATENT || (p.flags & XKV_FLAG_LOGITS_ONLY)) return false;
   if (p.dtype != XKV_BF16 && p.dtype != XKV_F16) return false;
   if (p.v_rank % 128 != 0 || p.v_rank > 1024 || p.logit_cap > 0.f || p.tail_dim != 0) return false;
+  if (p.mask) return false;   // additive masks run on the portable kernels
   if (!aligned16(p.v) || !stride_ok(p.v_sl) || (p.batch > 1 && !stride_ok(p.v_sb))) return false;
   return true;
 }

@@ -777,6 +777,7 @@ bool recon_tc_supported(const xkv_decode_params& p) {
   if (G != 4 && G != 8) return false;
   if (p.k_rank < BK || p.k_rank % BK != 0) return false;
   if (p.tail_dim != 0 || p.logit_cap > 0.f) return false;
+  if (p.mask) return false;   // additive masks run on the portable kernels
   if (p.rope_table) return false;   // caller-made tables go through the portable kernel
   if (p.q_sh % 8 != 0 || (p.batch > 1 && p.q_sb % 8 != 0)) return false;
   if (p.kp_sd != 1 || !aligned16(p.k) || !aligned16(p.k_proj) || !aligned16(p.q)) return false;

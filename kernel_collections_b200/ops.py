@@ -49,6 +49,7 @@ def build_params(
     rope_table: Optional[torch.Tensor] = None,   # (L, D/2, 2) fp32 {cos, sin}
     kv_lens: Optional[torch.Tensor] = None,      # (b,) int32: per-row cache lengths (ragged batches)
     return_lse: bool = False,                    # also return the (b, H) fp32 log-sum-exp of the scaled logits
+    mask: Optional[torch.Tensor] = None,         # additive, broadcastable to (b, H, L), same dtype
 ):
     """Validate shapes and fill one xkv_decode_params block.  Returns (params, result tensor)."""
     _C.require_cuda(q, k, v, k_proj, v_proj, q_tail, k_tail, out)
@@ -153,6 +154,18 @@ def build_params(
             keep.append(f)
             p.inv_freq = f.data_ptr()
 
+    if mask is not None:
+        _C.require_cuda(mask)
+        if mask.dtype != q.dtype:
+            mask = mask.to(q.dtype)
+        try:
+            m3 = mask.expand(b, H, L)
+        except RuntimeError:
+            raise ValueError(f"attn_mask of shape {tuple(mask.shape)} does not broadcast to ({b}, {H}, {L})") from None
+        if m3.stride(2) != 1 and L != 1:
+            m3 = m3.contiguous()
+        keep.append(m3)
+        p.mask, p.mask_sb, p.mask_sh = m3.data_ptr(), m3.stride(0), m3.stride(1)
     if kv_lens is not None:
         _C.require_cuda(kv_lens)
         if kv_lens.dtype != torch.int32 or tuple(kv_lens.shape) != (b,) or not kv_lens.is_contiguous():

@@ -83,7 +83,7 @@ def test_cpu_tensors_are_rejected_loudly():
     kv = torch.randn(1, 2, 8, 16)
     with pytest.raises(RuntimeError, match="CUDA"):
         K.group_query_attention(q, kv, kv)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(RuntimeError, match="CUDA"):
         K.group_query_attention(q, kv, kv, attn_mask=torch.zeros(1, 1, 1, 8))
     with pytest.raises(NotImplementedError):
         K.group_query_attention(q, kv, kv, dropout_p=0.1)

@@ -289,7 +289,9 @@ def test_error_behaviour_on_gpu():
     q = torch.randn(1, 4, 1, 16, device=DEV)
     kv = torch.randn(1, 2, 8, 16, device=DEV)
     with pytest.raises(NotImplementedError):
-        K.group_query_attention(q, kv, kv, attn_mask=torch.zeros(1, 1, 1, 8, device=DEV))
+        K.group_query_attention(q, kv, kv, dropout_p=0.5)
+    with pytest.raises(ValueError):
+        K.group_query_attention(q, kv, kv, attn_mask=torch.zeros(1, 1, 1, 9, device=DEV))
     with pytest.raises(ValueError):
         K.group_query_attention(q, kv.half(), kv.half())
     with pytest.raises(AssertionError):
@@ -331,3 +333,47 @@ def test_prefill_decode_separated_buffers(dtype):
                         v=vpd, sm_scale=0.2, return_lse=True)
     s = torch.einsum("bhd,blkd->bhl", q.float(), kp.float()) * 0.2
     assert (lse.cpu() - torch.logsumexp(s, -1)).abs().max().item() < (2e-2 if dtype != torch.float32 else 1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_additive_attention_mask(dtype):
+    """attn_mask is added to the scaled logits before the softmax (attention.py:60-64), in every
+    broadcast form the reference accepts; also on factorized caches and on head_dim-128 shapes,
+    where masked calls leave the tensor-core kernels for the portable ones."""
+    b, H, KVH, D, L, R = 2, 8, 2, 128, 200, 64
+    gen = g(11)
+    q, qd = mk((b, H, 1, D), dtype, gen=gen)
+    k, kd = mk((b, KVH, L, D), dtype, gen=gen)
+    v, vd = mk((b, KVH, L, D), dtype, gen=gen)
+    G = H // KVH
+
+    def ref_dense(mask5):
+        qq = q.float().view(b, KVH, G, D)
+        s = torch.matmul(qq, k.float().transpose(-1, -2)) / D ** 0.5 + mask5.float()[:, :, :, 0]
+        p = torch.softmax(s, -1)
+        return torch.matmul(p, v.float()).view(b, H, 1, D)
+
+    for shape in [(b, 1, 1, 1, L), (b, KVH, G, 1, L), (1, 1, 1, 1, L)]:
+        m, md = mk(shape, dtype, 2.0, gen=gen)
+        m5 = m.expand(b, KVH, G, 1, L)
+        check(K.group_query_attention(qd, kd, vd, attn_mask=md), ref_dense(m5), dtype, f"mask {shape}")
+    m4, m4d = mk((b, H, 1, L), dtype, 2.0, gen=gen)
+    check(K.group_query_attention_sdpa(qd, kd, vd, attn_mask=m4d), ref_dense(m4.view(b, KVH, G, 1, L)), dtype, "mask 4-D")
+    # a padding-style mask equals truncating the cache
+    pad = torch.zeros(b, 1, 1, L)
+    pad[0, ..., 150:] = float("-inf")
+    got = K.group_query_attentionv2(qd, kd, vd, attn_mask=pad.to(dtype).to(DEV))
+    lens = torch.tensor([150, L], dtype=torch.int32, device=DEV)
+    check(got, K.group_query_attention(qd, kd, vd, kv_lens=lens).float().cpu(), dtype, "-inf mask vs kv_lens")
+    # factorized cache
+    Ak, Akd = mk((b, L, R), dtype, gen=gen)
+    Bk, Bkd = mk((b, KVH, R, D), dtype, R ** -0.5, gen=gen)
+    Av, Avd = mk((b, L, R), dtype, gen=gen)
+    Bv, Bvd = mk((b, KVH, R, D), dtype, R ** -0.5, gen=gen)
+    m, md = mk((b, 1, 1, 1, L), dtype, 2.0, gen=gen)
+    Kf = torch.matmul(Ak.float().unsqueeze(1), Bk.float())
+    Vf = torch.matmul(Av.float().unsqueeze(1), Bv.float())
+    qq = q.float().view(b, KVH, G, D)
+    s = torch.matmul(qq, Kf.transpose(-1, -2)) / D ** 0.5 + m.float()[:, :, :, 0]
+    want = torch.matmul(torch.softmax(s, -1), Vf).view(b, H, 1, D)
+    check(K.group_query_attention_factorized(qd, Akd, Bkd, Avd, Bvd, attn_mask=md), want, dtype, "masked factorized")
