@@ -11,6 +11,7 @@
 // The logits round trip costs 8 bytes per (head, token) of HBM traffic, a few percent of the latent
 // rows it sits next to.
 #include "xkv_internal.h"
+#include <stdlib.h>
 
 namespace xkv {
 
@@ -61,8 +62,16 @@ bool two_pass_plan(const xkv_decode_params* layers, int n, TwoPassPlan* pl) {
   pl->off_logits = off;
   off += align_up((size_t)p.batch * heads * p.kv_len * sizeof(float), 256);
   pl->off_pass2 = off;
-  if (!latent_pv_plan(p, heads, &pl->pv)) return false;
-  off += pl->pv.total_bytes;
+  // second pass: tcgen05 kernel with the output in TMEM; XKV_PV_MMA_SYNC=1 keeps the mma.sync one
+  const char* e = getenv("XKV_PV_MMA_SYNC");
+  pl->use_pv_tc = (pv_tc_supported(p) && !(e && e[0] == '1')) ? 1 : 0;
+  if (pl->use_pv_tc) {
+    if (!pv_tc_plan(p, heads, &pl->pv_tc)) return false;
+    off += pl->pv_tc.total_bytes;
+  } else {
+    if (!latent_pv_plan(p, heads, &pl->pv)) return false;
+    off += pl->pv.total_bytes;
+  }
   pl->total_bytes = off;
   return true;
 }
@@ -87,13 +96,17 @@ int two_pass_decode(const xkv_decode_params* layers, int n, const TwoPassPlan& p
   // the first pass cleared the status words at the head of the workspace; the second pass reports
   // into the same words (the first failure wins)
   int* status = reinterpret_cast<int*>(w);
-  rc = latent_pv_run(p, heads, pl.pv, logits, w + pl.off_pass2, status, st);
+  rc = pl.use_pv_tc ? pv_tc_run(p, heads, pl.pv_tc, logits, w + pl.off_pass2, status, st)
+                    : latent_pv_run(p, heads, pl.pv, logits, w + pl.off_pass2, status, st);
   if (rc != XKV_OK) return rc;
-  const float* partial = reinterpret_cast<const float*>(w + pl.off_pass2 + pl.pv.off_partial);
-  const float* lse = reinterpret_cast<const float*>(w + pl.off_pass2 + pl.pv.off_lse);
+  const size_t off_partial = pl.use_pv_tc ? pl.pv_tc.off_partial : pl.pv.off_partial;
+  const size_t off_lse = pl.use_pv_tc ? pl.pv_tc.off_lse : pl.pv.off_lse;
+  const int pv_splits = pl.use_pv_tc ? pl.pv_tc.num_splits : pl.pv.num_splits;
+  const float* partial = reinterpret_cast<const float*>(w + pl.off_pass2 + off_partial);
+  const float* lse = reinterpret_cast<const float*>(w + pl.off_pass2 + off_lse);
   for (int i = 0; i < n; ++i) {
     const xkv_decode_params& li = layers[i];
-    rc = launch_merge(partial, lse, li.out, p.dtype, p.batch, H, pl.pv.num_splits, p.v_rank, li.value_dim, li.v_proj,
+    rc = launch_merge(partial, lse, li.out, p.dtype, p.batch, H, pv_splits, p.v_rank, li.value_dim, li.v_proj,
                       li.v_proj ? li.v_proj_heads : 1, li.vp_sb, li.vp_sh, li.vp_sr, li.vp_sd, li.o_sb, li.o_sh, st,
                       heads, i * H, li.lse_out, li.lse_sb);
     if (rc != XKV_OK) return rc;

@@ -89,12 +89,24 @@ bool latent_pv_plan(const xkv_decode_params& p, int heads, LatentTcPlan* plan);
 int latent_pv_run(const xkv_decode_params& p, int heads, const LatentTcPlan& plan, const float* logits, void* ws,
                   int* status, cudaStream_t st);
 
+// ---- tcgen05 softmax + P.A_v pass with the output in TMEM (pv_tc_sm100.cu) ------------------------
+struct PvTcPlan {
+  int col_blocks, head_blocks, tiles, num_splits;
+  size_t off_partial, off_lse, total_bytes;
+};
+bool pv_tc_supported(const xkv_decode_params& p);
+bool pv_tc_plan(const xkv_decode_params& p, int heads, PvTcPlan* plan);
+int pv_tc_run(const xkv_decode_params& p, int heads, const PvTcPlan& plan, const float* logits, void* ws,
+              int* status, cudaStream_t st);
+
 // ---- two-pass decode for factorized values behind dense / RoPE-reconstructed keys (two_pass.cu)
 struct TwoPassPlan {
   int heads;                 // layers x heads, stacked for the second pass
   ReconTcPlan recon;
   DenseTcPlan dense;
-  LatentTcPlan pv;
+  LatentTcPlan pv;           // second pass on mma.sync (XKV_PV_MMA_SYNC=1), or
+  PvTcPlan pv_tc;            // on tcgen05 with the output in TMEM
+  int use_pv_tc;
   size_t off_logits, off_pass1, off_pass2, total_bytes;
 };
 bool two_pass_supported(const xkv_decode_params* layers, int n);
