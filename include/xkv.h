@@ -63,6 +63,12 @@ typedef enum xkv_value_mode {
 #define XKV_FLAG_LOGITS_ONLY 1u  /* write sm_scale * logits to `logits`, skip softmax and P.V */
 #define XKV_FLAG_FORCE_GENERIC 2u /* use the portable CUDA-core kernel even when a tensor-core
                                      kernel covers the shape (debugging / cross-checks)      */
+#define XKV_FLAG_RECON_SINGLE_CTA 4u /* key reconstruction: keep one CTA per tile instead of CTA
+                                     pairs that share each MMA (cross-checks)                */
+#define XKV_FLAG_PV_MMA_SYNC 8u  /* two-pass decode: run the softmax + P.A_v pass on the mma.sync
+                                     kernel instead of the tcgen05 one (cross-checks)         */
+#define XKV_FLAG_RECON_PAIR 16u  /* key reconstruction: ask for the CTA-pair variant where the
+                                     library would not choose it by itself                    */
 
 /*
  * One decode-attention call.  Shapes (H = num_heads, KVH = num_kv_heads, L = kv_len):
@@ -225,6 +231,31 @@ XKV_API int xkv_merge(const float* partial_o, const float* lse, void* out, int d
  * Replaces flash_recontruction/rope/sin_cos.py:72-99 (rotary_sin_cos). */
 XKV_API int xkv_rope_table(float* cos_sin, int kv_len, int half, int pos_offset, float theta,
                    const float* inv_freq, void* stream);
+
+/*
+ * Rotate the decode-step queries to their positions: out[b, h, :] = RoPE(q[b, h, :], pos_b) in the
+ * half-split form (pairs j, j + head_dim/2), angle = float(pos_b) * inv_freq[j].  pos_b is
+ * positions[b] (device int32, one per batch row) when positions != NULL, else `position`.  q and out
+ * are (batch, num_heads, head_dim) of `dtype` with element strides; out may alias q.  inv_freq may be
+ * NULL (derived from theta).  Replaces the rotation the caller of the reference's kernels does itself
+ * with flash_recontruction/rope/rope_ref.py:11-21 (the kernels use q as given, qAB/v1.py:71-77).
+ */
+XKV_API int xkv_rope_query(const void* q, void* out, int dtype, int batch, int num_heads, int head_dim,
+                   int64_t q_sb, int64_t q_sh, int64_t o_sb, int64_t o_sh, int position,
+                   const int32_t* positions, float theta, const float* inv_freq, void* stream);
+
+/*
+ * Append one token per sequence to a factorized cache: latent[b, pos_b, :] = x[b, :] . proj, with x
+ * (batch, in_dim) the new key (or value) row of all KV heads side by side, proj (in_dim, rank) the
+ * map into latent space (the pseudo-inverse of the cache's B matrix) addressed as
+ * proj[c * p_sc + r * p_sr], and latent (batch, capacity, rank) the cache's A.  pos_b as in
+ * xkv_rope_query; rows whose position is outside [0, capacity) are left alone.  fp32 accumulation.
+ * The reference has no counterpart: its caches are synthetic and never grow
+ * (flash_decoding/gqa.py:60,89 take one constant length).
+ */
+XKV_API int xkv_latent_append(const void* x, int64_t x_sb, const void* proj, int64_t p_sc, int64_t p_sr,
+                      void* latent, int64_t l_sb, int64_t l_sl, const int32_t* positions, int position,
+                      int dtype, int batch, int in_dim, int rank, int capacity, void* stream);
 
 #ifdef __cplusplus
 }

@@ -16,7 +16,7 @@ from . import build as _build
 XKV_F32, XKV_BF16, XKV_F16 = 0, 1, 2
 SCORE_DENSE, SCORE_LATENT, SCORE_RECON_ROPE, SCORE_RECON = 0, 1, 2, 3
 VALUE_DENSE, VALUE_LATENT = 0, 1
-FLAG_LOGITS_ONLY, FLAG_FORCE_GENERIC = 1, 2
+FLAG_LOGITS_ONLY, FLAG_FORCE_GENERIC, FLAG_RECON_SINGLE_CTA, FLAG_PV_MMA_SYNC, FLAG_RECON_PAIR = 1, 2, 4, 8, 16
 
 _DTYPES = {torch.float32: XKV_F32, torch.bfloat16: XKV_BF16, torch.float16: XKV_F16}
 
@@ -25,7 +25,7 @@ EXPORTS = [
     "xkv_workspace_status", "xkv_decode_builtin_scratch",
     "xkv_dense_decode", "xkv_absorbed_decode", "xkv_recon_rope_decode", "xkv_qab_logits",
     "xkv_mla_decode", "xkv_group_decode_workspace_bytes", "xkv_group_decode", "xkv_merge",
-    "xkv_rope_table",
+    "xkv_rope_table", "xkv_rope_query", "xkv_latent_append",
 ]
 
 
@@ -102,6 +102,13 @@ def load():
                                   C.c_int, C.c_int64, C.c_int64, C.c_void_p]
         lib.xkv_rope_table.restype = C.c_int
         lib.xkv_rope_table.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
+        lib.xkv_rope_query.restype = C.c_int
+        lib.xkv_rope_query.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64,
+                                       C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p]
+        lib.xkv_latent_append.restype = C.c_int
+        lib.xkv_latent_append.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64,
+                                          C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                          C.c_void_p]
         lib.xkv_decode_params_size.restype = C.c_size_t
         lib.xkv_decode_builtin_scratch.restype = C.c_int
         lib.xkv_decode_builtin_scratch.argtypes = [C.POINTER(DecodeParams), C.c_void_p]
@@ -136,9 +143,16 @@ def dtype_code(t: torch.Tensor) -> int:
 
 
 def require_cuda(*tensors):
+    dev = None
     for t in tensors:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise RuntimeError("kernel_collections_b200 runs on CUDA tensors only (no CPU fallback)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"all tensors of one call must live on one device; got {dev} and {t.device}")
 
 
 # ---- workspace: one grow-only byte buffer per (device, stream) ------------------------------
@@ -146,8 +160,7 @@ _workspaces: dict = {}
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    key = (device.index if device.index is not None else torch.cuda.current_device(),
-           torch.cuda.current_stream(device).cuda_stream)
+    key = (_device_of(device), torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
@@ -169,29 +182,64 @@ def inv_freq(dim: int, theta: float, device: torch.device) -> torch.Tensor:
     return t
 
 
-def run_decode(params: DecodeParams, device: torch.device, entry: str = "xkv_decode"):
+class DeviceTimeout(RuntimeError):
+    """A bounded device-side wait of a tensor-core kernel expired; the output of that call is not valid."""
+
+
+_check_status = os.environ.get("XKV_CHECK_STATUS", "0") not in ("", "0")
+
+
+def set_check_status(on: bool) -> bool:
+    """Turn the post-call status check on or off (default: the XKV_CHECK_STATUS environment variable
+    as it was when this module was imported, else off).  With it on, every decode call synchronises
+    its stream, reads the status words its kernels left in the workspace and raises DeviceTimeout
+    when a bounded wait gave up.  Returns the previous setting."""
+    global _check_status
+    prev, _check_status = _check_status, bool(on)
+    return prev
+
+
+def _device_of(device: torch.device) -> int:
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
+def raise_on_status(ws_ptr: int, stream: int, what: str):
+    """Read the status words at `ws_ptr` (synchronises `stream`) and raise if the call failed."""
+    detail = (C.c_int32 * 8)()
+    rc = load().xkv_workspace_status(ws_ptr, stream, detail)
+    if rc == -6:
+        d = list(detail)
+        raise DeviceTimeout(f"{what}: {strerror(rc)} (role {d[1]}, tile {d[2]}, chunk {d[3]}, step {d[4]}); "
+                            "the output of this call is not valid")
+    check(rc, what)
+
+
+def run_decode(params: DecodeParams, device: torch.device, entry: str = "xkv_decode", check_status=None):
     lib = load()
-    nbytes = lib.xkv_decode_workspace_bytes(C.byref(params))
-    if nbytes == 0:
-        # let the entry point produce the precise status
-        rc = getattr(lib, entry)(C.byref(params), None, 0, None)
-        check(rc if rc != 0 else -2, entry)
-    ws = workspace(device, nbytes)
-    stream = torch.cuda.current_stream(device).cuda_stream
-    rc = getattr(lib, entry)(C.byref(params), ws.data_ptr(), ws.numel(), stream)
-    check(rc, entry)
+    with torch.cuda.device(_device_of(device)):
+        nbytes = lib.xkv_decode_workspace_bytes(C.byref(params))
+        if nbytes == 0:
+            # let the entry point produce the precise status
+            rc = getattr(lib, entry)(C.byref(params), None, 0, None)
+            check(rc if rc != 0 else -2, entry)
+        ws = workspace(device, nbytes)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        rc = getattr(lib, entry)(C.byref(params), ws.data_ptr(), ws.numel(), stream)
+        check(rc, entry)
+        if _check_status if check_status is None else check_status:
+            raise_on_status(ws.data_ptr(), stream, entry)
 
 
 def last_status(device: torch.device):
     """Synchronise the current stream and return (status, detail[8]) of the last call that used
     this (device, stream) workspace."""
-    key = (device.index if device.index is not None else torch.cuda.current_device(),
-           torch.cuda.current_stream(device).cuda_stream)
+    key = (_device_of(device), torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None:
         return 0, [0] * 8
     detail = (C.c_int32 * 8)()
-    rc = load().xkv_workspace_status(buf.data_ptr(), key[1], detail)
+    with torch.cuda.device(key[0]):
+        rc = load().xkv_workspace_status(buf.data_ptr(), key[1], detail)
     return rc, list(detail)
 
 
@@ -200,10 +248,15 @@ BUILTIN_SCRATCH_BYTES = 8 << 20
 
 def run_decode_builtin_scratch(params: DecodeParams, device: torch.device):
     """Launch through xkv_decode_builtin_scratch: no workspace tensor, no allocation."""
-    rc = load().xkv_decode_builtin_scratch(C.byref(params), torch.cuda.current_stream(device).cuda_stream)
+    with torch.cuda.device(_device_of(device)):
+        rc = load().xkv_decode_builtin_scratch(C.byref(params), torch.cuda.current_stream(device).cuda_stream)
     check(rc, "xkv_decode_builtin_scratch")
 
 
-def plan_name(params: DecodeParams):
-    r = load().xkv_decode_plan(C.byref(params))
+def plan_name(params: DecodeParams, device=None):
+    if device is not None and device.type == "cuda":
+        with torch.cuda.device(_device_of(device)):
+            r = load().xkv_decode_plan(C.byref(params))
+    else:
+        r = load().xkv_decode_plan(C.byref(params))
     return r.decode() if r else None

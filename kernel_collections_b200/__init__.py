@@ -15,6 +15,7 @@ from .attention import (  # noqa: F401
     group_query_attention_factorized_RoPE,
     recon_rope_decode,
     rope_query,
+    latent_append,
     xkv_group_decode,
     mla_absorbed_decode,
 )

@@ -157,7 +157,8 @@ def group_query_attention_factorized_RoPE(query, key_A, key_B, value_A, value_B,
 
 # ---- entry points the reference does not have but its benchmark configurations need -------------
 def recon_rope_decode(query, key_A, key_B, value, value_B=None, *, theta, sm_scale=None,
-                      k_position_offset=0, num_splits=0, force_generic=False, kv_lens=None):
+                      k_position_offset=0, num_splits=0, force_generic=False, kv_lens=None, cta_pair=None,
+                      pv_mma_sync=False, check_status=None):
     """Factorized K + RoPE with dense V (bsz, num_kv_heads, kv_len, head_dim), or factorized V
     when value_B is given (then `value` is the value latent).  key_B may be (bsz|1, num_kv_heads,
     k_rank, head_dim) or a shared (k_rank, num_kv_heads*head_dim) matrix.  Default scale
@@ -166,8 +167,14 @@ def recon_rope_decode(query, key_A, key_B, value, value_B=None, *, theta, sm_sca
     D = q.shape[-1]
     key_B = as_key_proj(key_B, D)
     scale = D ** -0.5 if sm_scale is None else sm_scale
+    flags = 0
+    if cta_pair is not None:     # None: the library chooses; True / False pin the CTA-pair or single-CTA kernel
+        flags |= _C.FLAG_RECON_PAIR if cta_pair else _C.FLAG_RECON_SINGLE_CTA
+    if pv_mma_sync:              # factorized values: second pass on the mma.sync kernel (cross-checks)
+        flags |= _C.FLAG_PV_MMA_SYNC
     kw = dict(score_mode=_C.SCORE_RECON_ROPE, q=q, k=key_A, k_proj=key_B, sm_scale=scale, theta=theta,
-              pos_offset=k_position_offset, num_splits=num_splits, force_generic=force_generic, kv_lens=kv_lens)
+              pos_offset=k_position_offset, num_splits=num_splits, force_generic=force_generic, kv_lens=kv_lens,
+              extra_flags=flags, check_status=check_status)
     if value_B is None:
         o = ops.decode(entry="xkv_recon_rope_decode", value_mode=_C.VALUE_DENSE, v=value.transpose(1, 2), **kw)
     else:
@@ -184,18 +191,63 @@ def as_key_proj(B, head_dim):
     return B
 
 
-def rope_query(query, theta, position):
+def rope_query(query, theta, position, out=None):
     """Rotate a decode-step query (bsz, num_heads, 1, head_dim) to `position` (half-split RoPE,
-    flash_recontruction/rope/rope_ref.py:11-21).  Tiny; done with torch ops on the device."""
-    D = query.shape[-1]
-    f = _C.inv_freq(D, theta, query.device)
-    ang = torch.tensor(float(position), dtype=torch.float32, device=query.device) * f
-    cos = torch.cat((ang, ang)).cos()
-    sin = torch.cat((ang, ang)).sin()
-    x = query.float()
-    h = D // 2
-    rot = torch.cat((-x[..., h:], x[..., :h]), dim=-1)
-    return (x * cos + rot * sin).to(query.dtype)
+    flash_recontruction/rope/rope_ref.py:11-21) with the library's kernel (xkv_rope_query).
+    `position` is an int, or an int32 device tensor (bsz,) of per-sequence positions."""
+    _C.require_cuda(query)
+    q = query if query.stride(-1) == 1 else query.contiguous()
+    if q.dim() != 4 or q.shape[2] != 1:
+        raise ValueError(f"query must be (bsz, num_heads, 1, head_dim); got {tuple(query.shape)}")
+    b, H, _, D = q.shape
+    if out is None:
+        out = torch.empty((b, H, 1, D), dtype=q.dtype, device=q.device)
+    f = _C.inv_freq(D, theta, q.device)
+    pos_t, pos_i = None, 0
+    if isinstance(position, torch.Tensor):
+        if position.dtype != torch.int32 or tuple(position.shape) != (b,) or not position.is_cuda:
+            raise ValueError("per-sequence positions must be an int32 device tensor of shape (bsz,)")
+        pos_t = position.contiguous()
+    else:
+        pos_i = int(position)
+    with torch.cuda.device(q.device):
+        rc = _C.load().xkv_rope_query(q.data_ptr(), out.data_ptr(), _C.dtype_code(q), b, H, D, q.stride(0), q.stride(1),
+                                      out.stride(0), out.stride(1), pos_i, pos_t.data_ptr() if pos_t is not None else None,
+                                      float(theta), f.data_ptr(), torch.cuda.current_stream(q.device).cuda_stream)
+    _C.check(rc, "xkv_rope_query")
+    return out
+
+
+def latent_append(latent, new_rows, proj, position):
+    """Append one token per sequence to a factorized cache, in place: latent[b, pos_b] = new_rows[b] @ proj.
+
+    latent (bsz, capacity, rank) is the cache's A; new_rows (bsz, num_kv_heads * head_dim) the new key (or
+    value) rows; proj (num_kv_heads * head_dim, rank) the map into latent space, i.e. the pseudo-inverse of
+    the cache's (rank, num_kv_heads * head_dim) B matrix; `position` an int or an int32 device tensor
+    (bsz,) — typically the kv_lens of the step before.  Returns `latent`."""
+    _C.require_cuda(latent, new_rows, proj)
+    if latent.dim() != 3 or new_rows.dim() != 2 or proj.dim() != 2:
+        raise ValueError("latent (bsz, capacity, rank), new_rows (bsz, in_dim), proj (in_dim, rank) expected")
+    b, cap, R = latent.shape
+    if new_rows.shape[0] != b or proj.shape != (new_rows.shape[1], R):
+        raise ValueError("shape mismatch among latent, new_rows and proj")
+    if latent.stride(2) != 1 or not (latent.dtype == new_rows.dtype == proj.dtype):
+        raise ValueError("latent needs a contiguous last dim and all tensors one dtype")
+    x = new_rows if new_rows.stride(1) == 1 else new_rows.contiguous()
+    pos_t, pos_i = None, 0
+    if isinstance(position, torch.Tensor):
+        if position.dtype != torch.int32 or tuple(position.shape) != (b,) or not position.is_cuda:
+            raise ValueError("per-sequence positions must be an int32 device tensor of shape (bsz,)")
+        pos_t = position.contiguous()
+    else:
+        pos_i = int(position)
+    with torch.cuda.device(latent.device):
+        rc = _C.load().xkv_latent_append(x.data_ptr(), x.stride(0), proj.data_ptr(), proj.stride(0), proj.stride(1),
+                                         latent.data_ptr(), latent.stride(0), latent.stride(1),
+                                         pos_t.data_ptr() if pos_t is not None else None, pos_i, _C.dtype_code(latent),
+                                         b, x.shape[1], R, cap, torch.cuda.current_stream(latent.device).cuda_stream)
+    _C.check(rc, "xkv_latent_append")
+    return latent
 
 
 def xkv_group_decode(queries, key_A, key_Bs, value, value_Bs=None, *, theta, sm_scale=None,

@@ -2,8 +2,9 @@
 
     python -m kernel_collections_b200.build [--force] [--verbose]
 
-The library is compiled from kernel_collections_b200/csrc/*.cu and written next to this
-file; it is rebuilt only when a source or header is newer than the library.
+Every kernel_collections_b200/csrc/*.cu is compiled to an object file under csrc/build/ (in
+parallel, only when the source or a header is newer than the object) and the objects are linked
+into libxkv.so next to this file.
 """
 from __future__ import annotations
 
@@ -11,15 +12,17 @@ import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
+OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libxkv.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC",
+    "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
     "-Xcompiler", "-fvisibility=hidden",
 ]
 
@@ -28,17 +31,25 @@ def sources():
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
-def _deps():
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
-    deps.append(os.path.join(ROOT, "include", "xkv.h"))
-    return deps
+def _headers():
+    hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    hs.append(os.path.join(ROOT, "include", "xkv.h"))
+    return hs
+
+
+def _obj(src: str) -> str:
+    return os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+
+
+def _stale(target: str, deps) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(d) > t for d in deps)
 
 
 def needs_build() -> bool:
-    if not os.path.exists(LIB_PATH):
-        return True
-    t = os.path.getmtime(LIB_PATH)
-    return any(os.path.getmtime(d) > t for d in _deps())
+    return _stale(LIB_PATH, sources() + _headers())
 
 
 def find_nvcc() -> str:
@@ -48,19 +59,44 @@ def find_nvcc() -> str:
     return nvcc
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not needs_build():
-        return LIB_PATH
-    cmd = [find_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC]
+def build(force: bool = False, verbose: bool = False, defines=(), lib_path: str = LIB_PATH) -> str:
+    """Compile what is stale and link.  `defines` (e.g. ["XKV_TC_PROFILE"]) and another `lib_path`
+    give an instrumented copy of the library next to the regular one (objects are then rebuilt)."""
+    if not force and not defines and not needs_build():
+        return lib_path
+    nvcc = find_nvcc()
+    obj_dir = OBJ_DIR if not defines else OBJ_DIR + "_" + "_".join(defines)
+    os.makedirs(obj_dir, exist_ok=True)
+    base = [nvcc, *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC] + [f"-D{d}" for d in defines]
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += sources() + ["-o", LIB_PATH, "-lcudart"]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or proc.returncode != 0:
-        sys.stderr.write(proc.stdout + proc.stderr)
-    if proc.returncode != 0:
+        base += ["-Xptxas", "-v"]
+    hdrs = _headers()
+    jobs = []
+    for src in sources():
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
+        if force or _stale(obj, [src] + hdrs):
+            jobs.append((src, obj))
+
+    def compile_one(job):
+        src, obj = job
+        return src, subprocess.run(base + ["-c", src, "-o", obj], capture_output=True, text=True)
+
+    with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as pool:
+        results = list(pool.map(compile_one, jobs))
+    failed = False
+    for src, proc in results:
+        if verbose or proc.returncode != 0:
+            sys.stderr.write(f"--- {os.path.basename(src)}\n{proc.stdout}{proc.stderr}")
+        failed = failed or proc.returncode != 0
+    if failed:
         raise RuntimeError("nvcc failed building libxkv.so")
-    return LIB_PATH
+    objs = [os.path.join(obj_dir, os.path.basename(s)[:-3] + ".o") for s in sources()]
+    proc = subprocess.run([nvcc, "--shared", "-gencode", "arch=compute_100a,code=sm_100a", *objs, "-o", lib_path,
+                           "-lcudart"], capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError("linking libxkv.so failed")
+    return lib_path
 
 
 if __name__ == "__main__":

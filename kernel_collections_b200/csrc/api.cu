@@ -296,4 +296,21 @@ int xkv_rope_table(float* cos_sin, int kv_len, int half, int pos_offset, float t
                            static_cast<cudaStream_t>(stream));
 }
 
+int xkv_rope_query(const void* q, void* out, int dtype, int batch, int num_heads, int head_dim, int64_t q_sb,
+                   int64_t q_sh, int64_t o_sb, int64_t o_sh, int position, const int32_t* positions, float theta,
+                   const float* inv_freq, void* stream) {
+  if (!q || !out || batch <= 0 || num_heads <= 0 || head_dim <= 0 || (head_dim & 1)) return XKV_ERR_BAD_ARG;
+  if (!inv_freq && !(theta > 0.f)) return XKV_ERR_BAD_ARG;
+  return launch_rope_query(q, out, dtype, batch, num_heads, head_dim, q_sb, q_sh, o_sb, o_sh, position, positions,
+                           theta, inv_freq, static_cast<cudaStream_t>(stream));
+}
+
+int xkv_latent_append(const void* x, int64_t x_sb, const void* proj, int64_t p_sc, int64_t p_sr, void* latent,
+                      int64_t l_sb, int64_t l_sl, const int32_t* positions, int position, int dtype, int batch,
+                      int in_dim, int rank, int capacity, void* stream) {
+  if (!x || !proj || !latent || batch <= 0 || in_dim <= 0 || rank <= 0 || capacity <= 0) return XKV_ERR_BAD_ARG;
+  return launch_latent_append(x, x_sb, proj, p_sc, p_sr, latent, l_sb, l_sl, positions, position, dtype, batch,
+                              in_dim, rank, capacity, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

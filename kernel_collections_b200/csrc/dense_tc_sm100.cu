@@ -224,6 +224,18 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       pf[2] = pack2(p[0][2], p[0][3], T());
       pf[3] = pack2(p[1][2], p[1][3], T());
       // ---- O = O * alpha + P . V ---------------------------------------------------------------------
+      if (a.kv_lens != nullptr && (tile + 1) * TILE > row_len) {
+        // Ragged batch, last tile of the row: value rows past the row's own length are outside the
+        // call (they may hold anything, NaN included, and 0 * NaN is NaN).  Each warp zeroes those
+        // among its own 16 tokens before reading them.
+        const int first = max(row_len - tile * TILE, cw * 16);
+        for (int idx = lane; idx < (cw * 16 + 16 - first) * 16; idx += 32) {
+          const int token = first + (idx >> 4), ch = idx & 15;
+          const uint32_t za = sv + (ch >> 3) * (KV_BYTES / 2) + token * 128 + ((ch & 7) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(za), "r"(0u) : "memory");
+        }
+        __syncwarp();
+      }
       {
         const int mi = lane >> 3, r = lane & 7;
         const int token = cw * 16 + (mi & 1) * 8 + r;       // matrices 0/1: tokens 0-7 / 8-15 of dims n0..

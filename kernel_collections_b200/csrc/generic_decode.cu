@@ -230,11 +230,14 @@ decode_partial_kernel(const xkv_decode_params p, const PartialGeom g, const floa
       float mx = m_s[h];
 #pragma unroll
       for (int t = 0; t < TT; ++t) mx = fmaxf(mx, logit_s[h * TT + t]);
-      const float alpha = expf(m_s[h] - mx);  // exp(-inf) = 0 on the first tile
+      // a tile masked to -inf before anything finite was seen leaves the maximum at -inf: keep the
+      // exponentials finite (they are all zero) instead of forming exp(-inf - -inf)
+      const float m_use = (mx == -CUDART_INF_F) ? 0.f : mx;
+      const float alpha = (m_s[h] == -CUDART_INF_F) ? 0.f : expf(m_s[h] - m_use);
       float sum = 0.f;
 #pragma unroll
       for (int t = 0; t < TT; ++t) {
-        const float e = expf(logit_s[h * TT + t] - mx);
+        const float e = expf(logit_s[h * TT + t] - m_use);
         prob_s[h * TT + t] = e;
         sum += e;
       }
@@ -429,15 +432,20 @@ int run_generic(const xkv_decode_params& p, const GenericPlan& pl, void* ws, cud
 }  // namespace
 
 int device_sm_count() {
-  static int cached = 0;
-  if (cached) return cached;
+  // SM count of the current device, looked up once per device
+  constexpr int kMaxDevices = 64;
+  static int cached[kMaxDevices] = {};
   int dev = 0, n = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess ||
-      cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+  if (cudaGetDevice(&dev) != cudaSuccess) {
     cudaGetLastError();
     return kNumSMsFallback;
   }
-  cached = n;
+  if (dev >= 0 && dev < kMaxDevices && cached[dev] > 0) return cached[dev];
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return kNumSMsFallback;
+  }
+  if (dev >= 0 && dev < kMaxDevices) cached[dev] = n;
   return n;
 }
 

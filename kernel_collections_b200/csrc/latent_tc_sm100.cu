@@ -325,6 +325,18 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             acc[m][n][2] *= alpha[m][1]; acc[m][n][3] *= alpha[m][1];
           }
       }
+      if (a.kv_lens != nullptr && (tile + 1) * TILE > row_len) {
+        // Ragged batch, last tile of the row: latent rows past the row's own length are outside the
+        // call (they may hold anything, NaN included, and 0 * NaN is NaN).  Each warp zeroes its own
+        // value columns of those rows; every score read of this tile is behind barrier (B).
+        const int first = max(row_len - tile * TILE, 0), chunks = a.rv / 64;
+        for (int idx = lane; idx < (TILE - first) * chunks; idx += 32) {
+          const int token = first + idx / chunks, col = cw * (a.rv / 8) + (idx % chunks) * 8;
+          const uint32_t za = ss + (vblk0 + (col >> 6)) * BLK + swz(token, (col & 63) * 2);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(za), "r"(0u) : "memory");
+        }
+        __syncwarp();
+      }
 #pragma unroll
       for (int ks = 0; ks < TILE / 16; ++ks) {
         uint32_t pa[MT][4];

@@ -221,6 +221,21 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap tmV, const Args a) {
         l_sum *= alpha;
         m_ref = m_new;
       }
+      if (a.kv_lens != nullptr && (tile + 1) * TK > row_len) {
+        // Ragged batch, last tile of the row: value rows past the row's own length are outside the
+        // call (they may hold anything, NaN included, and 0 * NaN is NaN).  Once the tile has landed
+        // the softmax threads zero those rows; the proxy fence before the P hand-over below orders
+        // the stores ahead of the MMAs that read the tile.
+        const int it = tile - tile_begin, vstage = it % STAGES;
+        if (!mbar_wait(bar_vfull(vstage), (uint32_t)(it / STAGES) & 1u, abort_flag))
+          report(a.status, XKV_ERR_TIMEOUT, 26, tile, cb, b);
+        const int first = max(row_len - tile * TK, 0), per_row = (nc / 64) * 8;
+        for (int idx = r; idx < (TK - first) * per_row; idx += 128) {
+          const int row = first + idx / per_row, rem = idx % per_row;
+          *reinterpret_cast<uint4*>(sm + OFF_V + vstage * STAGE_BYTES + (rem >> 3) * BOX_BYTES + row * 128 + (rem & 7) * 16) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
       // ---- P row -> shared memory (K-major, 128-byte swizzle), row sum of the rounded values ----------
       if (!mbar_wait(bar_pempty(pbuf), pph ^ 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 24, tile, cb, b);
       const float mref = m_ref == -CUDART_INF_F ? 0.f : m_ref;

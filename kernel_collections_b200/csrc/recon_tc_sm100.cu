@@ -18,7 +18,6 @@
 // it gave up in the status words of the workspace, lets every role drain to the common exit,
 // waits for copies in flight, frees its TMEM and returns.  No TMA load uses cluster multicast.
 #include "sm100_common.cuh"
-#include <stdlib.h>
 
 namespace xkv {
 using namespace sm100;
@@ -599,6 +598,19 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
             const uint32_t v_base = base + OFF_V + slot * V_SLOT;
             // ldmatrix row of this lane: matrix mi = lane / 8, row r = lane % 8
             const int mi = lane >> 3, r = lane & 7;
+            if (a.kv_lens != nullptr && (tile + 1) * TILE_M > row_len) {
+              // Ragged batch, last tile of the row: cache rows past the row's own length are outside
+              // the call (they may hold anything, NaN included, and 0 * NaN is NaN).  This warp zeroes
+              // the 32 value columns it reads itself, so no other warp has to wait for it.
+              const int first = max(row_len - tile * TILE_M, 0);
+              for (int idx = lane; idx < (TILE_M - first) * 4; idx += 32) {
+                const int token = first + (idx >> 2), dim = pw * 32 + (idx & 3) * 8;
+                const uint32_t za = v_base + (dim >> 6) * (V_SLOT / 2) + token * 128 +
+                                    ((((dim & 63) >> 3) ^ (token & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(za), "r"(0u) : "memory");
+              }
+              __syncwarp();
+            }
 #pragma unroll
             for (int ks = 0; ks < TILE_M / 16; ++ks) {
               uint32_t b0 = 0, b1 = 0;
@@ -774,18 +786,17 @@ static int choose_splits(int rows, int tiles) {
   return best_s;
 }
 
-// Whether the CTA-pair (cta_group::2) variant serves a call.  It is parity-tested but measured no
-// faster than single CTAs while the epilogue paces the kernel (halving the B traffic does not
-// shorten the critical path), so it is opt-in: XKV_RECON_PAIR=1, and at least two tiles per row.
-static bool want_pair(int tiles) {
-  const char* e = getenv("XKV_RECON_PAIR");
-  return e != nullptr && e[0] == '1' && tiles >= 2;
+// Whether the CTA-pair (cta_group::2) variant serves a call: on request (XKV_FLAG_RECON_PAIR), with at
+// least two tiles per row, unless the caller pins single CTAs (XKV_FLAG_RECON_SINGLE_CTA).
+static bool want_pair(const xkv_decode_params& p, int tiles) {
+  if (p.flags & XKV_FLAG_RECON_SINGLE_CTA) return false;
+  return (p.flags & XKV_FLAG_RECON_PAIR) != 0 && tiles >= 2;
 }
 
 static bool plan_layers(const xkv_decode_params& p, int num_layers, ReconTcPlan* pl) {
   const int tiles = ceil_div(p.kv_len, TILE_M);
   const int rows = p.batch * num_layers;
-  pl->pair = want_pair(tiles) ? 1 : 0;
+  pl->pair = want_pair(p, tiles) ? 1 : 0;
   if (pl->pair) {
     // splits are served by pairs of CTAs: SMs / 2 slots, each slot works through ceil(tiles / 2) rounds
     const int slots = device_sm_count() / 2;

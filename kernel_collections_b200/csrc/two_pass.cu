@@ -11,7 +11,6 @@
 // The logits round trip costs 8 bytes per (head, token) of HBM traffic, a few percent of the latent
 // rows it sits next to.
 #include "xkv_internal.h"
-#include <stdlib.h>
 
 namespace xkv {
 
@@ -62,9 +61,8 @@ bool two_pass_plan(const xkv_decode_params* layers, int n, TwoPassPlan* pl) {
   pl->off_logits = off;
   off += align_up((size_t)p.batch * heads * p.kv_len * sizeof(float), 256);
   pl->off_pass2 = off;
-  // second pass: tcgen05 kernel with the output in TMEM; XKV_PV_MMA_SYNC=1 keeps the mma.sync one
-  const char* e = getenv("XKV_PV_MMA_SYNC");
-  pl->use_pv_tc = (pv_tc_supported(p) && !(e && e[0] == '1')) ? 1 : 0;
+  // second pass: tcgen05 kernel with the output in TMEM; XKV_FLAG_PV_MMA_SYNC keeps the mma.sync one
+  pl->use_pv_tc = (pv_tc_supported(p) && !(p.flags & XKV_FLAG_PV_MMA_SYNC)) ? 1 : 0;
   if (pl->use_pv_tc) {
     if (!pv_tc_plan(p, heads, &pl->pv_tc)) return false;
     off += pl->pv_tc.total_bytes;

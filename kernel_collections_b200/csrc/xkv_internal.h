@@ -39,6 +39,14 @@ int launch_merge(const float* partial_o, const float* lse, void* out, int dtype,
 int launch_rope_table(float* cos_sin, int kv_len, int half, int pos_offset, float theta,
                       const float* inv_freq, cudaStream_t st);
 
+// ---- per-step state kernels (step_state.cu) ----------------------------------------------------
+int launch_rope_query(const void* q, void* out, int dtype, int batch, int num_heads, int head_dim, int64_t q_sb,
+                      int64_t q_sh, int64_t o_sb, int64_t o_sh, int position, const int32_t* positions, float theta,
+                      const float* inv_freq, cudaStream_t st);
+int launch_latent_append(const void* x, int64_t x_sb, const void* proj, int64_t p_sc, int64_t p_sr, void* latent,
+                         int64_t l_sb, int64_t l_sl, const int32_t* positions, int position, int dtype, int batch,
+                         int in_dim, int rank, int capacity, cudaStream_t st);
+
 // ---- tcgen05 key-reconstruction path (recon_tc_sm100.cu) ------------------------------------
 struct ReconTcPlan {
   int pair;             // CTA pairs (cta_group::2) instead of single CTAs

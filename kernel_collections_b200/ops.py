@@ -50,9 +50,10 @@ def build_params(
     kv_lens: Optional[torch.Tensor] = None,      # (b,) int32: per-row cache lengths (ragged batches)
     return_lse: bool = False,                    # also return the (b, H) fp32 log-sum-exp of the scaled logits
     mask: Optional[torch.Tensor] = None,         # additive, broadcastable to (b, H, L), same dtype
+    extra_flags: int = 0,                        # XKV_FLAG_* bits beyond logits-only / force-generic
 ):
     """Validate shapes and fill one xkv_decode_params block.  Returns (params, result tensor)."""
-    _C.require_cuda(q, k, v, k_proj, v_proj, q_tail, k_tail, out)
+    _C.require_cuda(q, k, v, k_proj, v_proj, q_tail, k_tail, out, rope_table, kv_lens, mask)
     # projections are addressed with a full set of strides; the streamed tensors need a
     # contiguous innermost dimension
     q, k, v, q_tail, k_tail = map(_inner_contig, (q, k, v, q_tail, k_tail))
@@ -63,7 +64,8 @@ def build_params(
     p = _C.DecodeParams()
     p.dtype = _C.dtype_code(q)
     p.score_mode, p.value_mode = score_mode, value_mode
-    p.flags = (_C.FLAG_LOGITS_ONLY if logits_only else 0) | (_C.FLAG_FORCE_GENERIC if force_generic else 0)
+    p.flags = (_C.FLAG_LOGITS_ONLY if logits_only else 0) | (_C.FLAG_FORCE_GENERIC if force_generic else 0) \
+        | int(extra_flags)
     b, H, D = q.shape
     L = k.shape[1]
     p.batch, p.num_heads, p.kv_len, p.head_dim = b, H, L, D
@@ -195,10 +197,12 @@ def build_params(
     return p, result
 
 
-def decode(*, entry: str = "xkv_decode", **kw):
-    """One decode-attention call through the C ABI entry point `entry`."""
+def decode(*, entry: str = "xkv_decode", check_status=None, **kw):
+    """One decode-attention call through the C ABI entry point `entry`.  check_status=True
+    synchronises after the call and raises _C.DeviceTimeout if a bounded device-side wait expired
+    (default: the process-wide setting, see _C.set_check_status)."""
     p, result = build_params(**kw)
-    _C.run_decode(p, kw["q"].device, entry)
+    _C.run_decode(p, kw["q"].device, entry, check_status)
     return result
 
 
@@ -231,10 +235,10 @@ def merge_segments(outs, lses):
 def plan(**kw):
     """Name of the kernel family the library would run for these arguments."""
     p, _ = build_params(**kw)
-    return _C.plan_name(p)
+    return _C.plan_name(p, kw["q"].device)
 
 
-def group_decode(layer_kwargs: list):
+def group_decode(layer_kwargs: list, check_status=None):
     """Run xkv_group_decode over per-layer keyword sets of decode() (same shapes, shared latents).
     Returns the list of per-layer outputs."""
     blocks, outs = [], []
@@ -246,10 +250,14 @@ def group_decode(layer_kwargs: list):
     arr = (_C.DecodeParams * n)(*blocks)
     lib = _C.load()
     dev = layer_kwargs[0]["q"].device
-    nbytes = lib.xkv_group_decode_workspace_bytes(arr, n)
-    if nbytes == 0:
-        _C.check(lib.xkv_group_decode(arr, n, None, 0, None) or -2, "xkv_group_decode")
-    ws = _C.workspace(dev, nbytes)
-    rc = lib.xkv_group_decode(arr, n, ws.data_ptr(), ws.numel(), torch.cuda.current_stream(dev).cuda_stream)
-    _C.check(rc, "xkv_group_decode")
+    with torch.cuda.device(dev):
+        nbytes = lib.xkv_group_decode_workspace_bytes(arr, n)
+        if nbytes == 0:
+            _C.check(lib.xkv_group_decode(arr, n, None, 0, None) or -2, "xkv_group_decode")
+        ws = _C.workspace(dev, nbytes)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = lib.xkv_group_decode(arr, n, ws.data_ptr(), ws.numel(), stream)
+        _C.check(rc, "xkv_group_decode")
+        if _C._check_status if check_status is None else check_status:
+            _C.raise_on_status(ws.data_ptr(), stream, "xkv_group_decode")
     return outs

@@ -377,3 +377,98 @@ def test_additive_attention_mask(dtype):
     s = torch.matmul(qq, Kf.transpose(-1, -2)) / D ** 0.5 + m.float()[:, :, :, 0]
     want = torch.matmul(torch.softmax(s, -1), Vf).view(b, H, 1, D)
     check(K.group_query_attention_factorized(qd, Akd, Bkd, Avd, Bvd, attn_mask=md), want, dtype, "masked factorized")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_leading_minus_inf_mask_single_split(dtype):
+    """A left-padding mask: the first 40 tokens are -inf, so whole 16-token tiles are masked before
+    the split has seen a finite logit.  With one KV split nothing may be dropped: the result equals
+    attention over the unmasked suffix."""
+    b, H, KVH, D, L, pad = 2, 8, 2, 64, 200, 40
+    gen = g(12)
+    q, qd = mk((b, H, D), dtype, gen=gen)
+    k, kd = mk((b, L, KVH, D), dtype, gen=gen)
+    v, vd = mk((b, L, KVH, D), dtype, gen=gen)
+    mask = torch.zeros(b, 1, L)
+    mask[:, :, :pad] = float("-inf")
+    for splits in (1, 0):
+        got = ops.decode(entry="xkv_dense_decode", score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, q=qd, k=kd, v=vd,
+                         sm_scale=D ** -0.5, mask=mask.to(dtype).to(DEV), num_splits=splits)
+        want = O.flash_decode_gqa(q, k[:, pad:], v[:, pad:], sm_scale=D ** -0.5)
+        check(got, want, dtype, f"leading -inf mask, num_splits={splits}")
+    # the most negative finite fp32 value rounds to -inf in bf16: same result
+    big = torch.zeros(b, 1, L)
+    big[:, :, :pad] = torch.finfo(torch.float32).min
+    got = ops.decode(entry="xkv_dense_decode", score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, q=qd, k=kd, v=vd,
+                     sm_scale=D ** -0.5, mask=big.to(DEV), num_splits=1)
+    check(got, want, dtype, "finfo.min mask")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rope_query_kernel_positions(dtype):
+    """xkv_rope_query: one position for the batch or one per sequence, in place or into a new tensor,
+    against the reference's rotation (flash_recontruction/rope/rope_ref.py:11-21).  The angles are formed
+    as in the oracle, so the result agrees to the last bit of the working dtype for bf16 / fp16 and to
+    fp32 rounding of cos / sin otherwise."""
+    b, H, D = 3, 8, 128
+    q, qd = mk((b, H, 1, D), dtype, gen=g(14))
+    for theta, pos in [(5e5, 16384), (1e7, 131072), (1e4, 0)]:
+        got = K.rope_query(qd, theta, pos)
+        want = O.rope_query(q, theta, pos)
+        if dtype == torch.float32:
+            assert (got.cpu() - want).abs().max().item() < 2e-6
+        else:
+            assert torch.equal(got.cpu(), want)
+    positions = torch.tensor([5, 70000, 131071], dtype=torch.int32, device=DEV)
+    got = K.rope_query(qd, 5e5, positions)
+    for i, pz in enumerate(positions.tolist()):
+        want = O.rope_query(q[i:i + 1], 5e5, pz)
+        assert (got[i:i + 1].float().cpu() - want.float()).abs().max().item() <= (2e-6 if dtype == torch.float32 else 0.0)
+    buf = qd.clone()
+    assert K.rope_query(buf, 5e5, positions, out=buf) is buf and torch.equal(buf, got)
+    with pytest.raises(ValueError):
+        K.rope_query(qd, 5e5, positions.long())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_latent_append_roundtrip(dtype):
+    """xkv_latent_append: the new token's key row projected with the pseudo-inverse of B lands in row
+    pos_b of the latent; with keys that lie in B's row space the appended row rebuilds the key, and a
+    decode over the grown cache equals the oracle on the cache extended on the CPU."""
+    b, KVH, D, R, cap, H = 3, 2, 64, 48, 40, 8
+    gen = g(15)
+    lens = [17, 0, 39]
+    Bm = torch.randn(R, KVH * D, generator=gen) / R ** 0.5
+    pinv = torch.linalg.pinv(Bm)                                         # (KVH*D, R)
+    A, Ad = mk((b, cap, R), dtype, gen=gen)
+    a_new = torch.randn(b, R, generator=gen)
+    k_new = (a_new @ Bm).to(dtype)                                       # in the row space of B (up to rounding)
+    pos = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    pinv_t = pinv.to(dtype)
+    out = K.latent_append(Ad, k_new.to(DEV), pinv_t.to(DEV), pos)
+    assert out is Ad
+    want_rows = (k_new.float() @ pinv_t.float())
+    ta = 1e-4 if dtype == torch.float32 else 2e-2
+    for i, n in enumerate(lens):
+        assert (Ad[i, n].float().cpu() - want_rows[i]).abs().max().item() <= ta * max(1.0, want_rows[i].abs().max().item())
+        keep = torch.ones(cap, dtype=torch.bool)
+        keep[n] = False
+        assert torch.equal(Ad[i, keep].cpu(), A[i, keep])              # nothing else was touched
+    if dtype == torch.float32:
+        assert (Ad[0, 17].cpu() @ Bm - k_new[0]).abs().max().item() < 1e-3   # the appended row rebuilds the key
+    # a position outside the cache appends nothing; a scalar position applies to every row
+    before = Ad.clone()
+    K.latent_append(Ad, k_new.to(DEV), pinv_t.to(DEV), torch.tensor([cap, -1, cap + 5], dtype=torch.int32, device=DEV))
+    assert torch.equal(before, Ad)
+    K.latent_append(Ad, k_new.to(DEV), pinv_t.to(DEV), 3)
+    assert (Ad[:, 3].float().cpu() - want_rows).abs().max().item() <= ta * max(1.0, want_rows.abs().max().item())
+    # decode over the grown cache (lengths + 1) against the oracle on the same latent bits
+    Bk = Bm.view(R, KVH, D).permute(1, 0, 2)[None].expand(b, -1, -1, -1).contiguous().to(dtype)
+    q, qd = mk((b, H, 1, D), dtype, gen=gen)
+    V, Vd = mk((b, cap, R), dtype, gen=gen)
+    new_lens = torch.tensor([n + 1 for n in lens], dtype=torch.int32, device=DEV)
+    got = K.group_query_attention_factorized(qd, Ad, Bk.to(DEV), Vd, Bk.to(DEV), kv_lens=new_lens)
+    Ac = Ad.cpu()
+    for i, n in enumerate(lens):
+        want = O.gqa_factorized(q[i:i + 1], Ac[i:i + 1, :n + 1], Bk[i:i + 1], V[i:i + 1, :n + 1], Bk[i:i + 1])
+        check(got[i:i + 1], want, dtype, f"decode after append, row {i}")

@@ -106,3 +106,64 @@ def test_zero_length_row_gives_zeros():
     assert (got[1] == 0).all() and (got[0] != 0).any() and (got[2] != 0).any()
     with pytest.raises(ValueError):
         K.group_query_attention(q, k, k, kv_lens=lens.long())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_tails_past_the_row_length_may_hold_nan(dtype):
+    """Cache rows at or past kv_lens[b] are outside the call: filling them with NaN must not change
+    any result, on every tensor-core kernel family (0 * NaN inside an MMA would poison the row)."""
+    LN = [1000, 1, 517, 128, 999, 64, 65]
+    b, G, L, R, Rv, theta = len(LN), 4, 1000, 128, 256, 500000.0
+    H = KVH * G
+    g = torch.Generator().manual_seed(65)
+    nan = float("nan")
+
+    def poisoned(t, axis):
+        t = t.clone()
+        for i, n in enumerate(LN):
+            idx = [slice(None)] * t.dim()
+            idx[0], idx[axis] = i, slice(n, None)
+            t[tuple(idx)] = nan
+        return t
+
+    q = torch.randn(b, H, 1, D, generator=g).to(dtype)
+    A = torch.randn(b, L, R, generator=g).to(dtype)
+    B = (torch.randn(R, KVH * D, generator=g) / R ** 0.5).to(dtype)
+    Bb = B.view(R, KVH, D).permute(1, 0, 2)[None].expand(b, -1, -1, -1).contiguous()
+    V = torch.randn(b, KVH, L, D, generator=g).to(dtype)
+    Kd = torch.randn(b, KVH, L, D, generator=g).to(dtype)
+    Av = torch.randn(b, L, Rv, generator=g).to(dtype)
+    Bv = (torch.randn(Rv, KVH * D, generator=g) / Rv ** 0.5).to(dtype)
+    Bvb = Bv.view(Rv, KVH, D).permute(1, 0, 2)[None].expand(b, -1, -1, -1).contiguous()
+    lens = torch.tensor(LN, dtype=torch.int32, device=DEV)
+    qd, Bd, Bvd, Bbd, Bvbd = (x.to(DEV) for x in (q, B, Bv, Bb, Bvb))
+    cases = {
+        "recon_tc (dense V)": lambda a, v, k, av: K.recon_rope_decode(qd, a, Bd, v, theta=theta, kv_lens=lens),
+        "recon_tc pair (dense V)": lambda a, v, k, av: K.recon_rope_decode(qd, a, Bd, v, theta=theta, kv_lens=lens, cta_pair=True),
+        "two-pass, tcgen05 second pass": lambda a, v, k, av: K.recon_rope_decode(qd, a, Bd, av, Bvd, theta=theta, kv_lens=lens),
+        "two-pass, mma.sync second pass": lambda a, v, k, av: K.recon_rope_decode(qd, a, Bd, av, Bvd, theta=theta, kv_lens=lens,
+                                                                                   pv_mma_sync=True),
+        "dense_tc": lambda a, v, k, av: K.group_query_attention(qd, k, v, kv_lens=lens),
+        "latent_tc": lambda a, v, k, av: K.group_query_attention_factorized(qd, a, Bbd, av, Bvbd, kv_lens=lens),
+    }
+    clean = (A.to(DEV), V.to(DEV), Kd.to(DEV), Av.to(DEV))
+    dirty = (poisoned(A, 1).to(DEV), poisoned(V, 2).to(DEV), poisoned(Kd, 2).to(DEV), poisoned(Av, 1).to(DEV))
+    for name, fn in cases.items():
+        want = fn(*clean)
+        got = fn(*dirty)
+        assert torch.isfinite(got.float()).all(), f"{name}: NaN leaked from rows past kv_lens"
+        assert torch.equal(got, want), f"{name}: rows past kv_lens changed the result"
+    # MLA (values alias the key latent) on the shared-latent kernel
+    Hm, lora, rope = 64, 128, 64
+    qn = torch.randn(b, Hm, lora, generator=g).to(dtype).to(DEV)
+    qr = (torch.randn(b, Hm, rope, generator=g) / 3).to(dtype).to(DEV)
+    c = (torch.randn(b, L, lora, generator=g) / 3).to(dtype)
+    kr = (torch.randn(b, L, rope, generator=g) / 3).to(dtype)
+    from kernel_collections_b200 import ops
+    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT, q=qn, q_tail=qr, sm_scale=0.1, num_kv_heads=1,
+              kv_lens=lens)
+    cd, krd = c.to(DEV), kr.to(DEV)
+    want = ops.decode(entry="xkv_mla_decode", k=cd, v=cd, k_tail=krd, **kw)
+    pc, pk = poisoned(c, 1).to(DEV), poisoned(kr, 1).to(DEV)
+    got = ops.decode(entry="xkv_mla_decode", k=pc, v=pc, k_tail=pk, **kw)
+    assert torch.isfinite(got.float()).all() and torch.equal(got, want), "MLA latent with NaN tails"

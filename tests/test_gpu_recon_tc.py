@@ -149,23 +149,23 @@ def test_group_decode_single_launch(dtype, NL, b, L, R, G):
 
 
 @pytest.mark.parametrize("case", [(2, 700, 128, 4), (1, 2048, 512, 8), (3, 129, 64, 4), (2, 4101, 256, 4)])
-def test_cta_pair_variant(monkeypatch, case):
-    """The opt-in CTA-pair variant (tcgen05 cta_group::2: two CTAs share every MMA, each loading half
+def test_cta_pair_variant(case):
+    """The CTA-pair variant (tcgen05 cta_group::2: two CTAs share every MMA, each loading half
     of the B chunk) must agree with the oracle and with the single-CTA kernel, odd tile counts and
     phantom tiles included."""
     b, L, R, G = case
     dtype, theta = torch.bfloat16, 500000.0
     q, A, B, V = make(b, L, R, G, dtype, seed=17)
     qd, Ad, Bd, Vd = q.to(DEV), A.to(DEV), B.to(DEV), V.to(DEV)
-    single = K.recon_rope_decode(qd, Ad, Bd, Vd.transpose(1, 2), theta=theta)
-    monkeypatch.setenv("XKV_RECON_PAIR", "1")
-    got = K.recon_rope_decode(qd, Ad, Bd, Vd.transpose(1, 2), theta=theta)
+    single = K.recon_rope_decode(qd, Ad, Bd, Vd.transpose(1, 2), theta=theta, cta_pair=False)
+    got = K.recon_rope_decode(qd, Ad, Bd, Vd.transpose(1, 2), theta=theta, cta_pair=True)
     status_ok()
     want = O.recon_rope_decode(q, A, b4(B, b), V.transpose(1, 2), theta)
     assert_close(got, want, "pair variant vs oracle")
     assert_close(got, single.float().cpu(), "pair variant vs single-CTA kernel", 4e-3, 2e-3)
-    assert torch.equal(got, K.recon_rope_decode(qd, Ad, Bd, Vd.transpose(1, 2), theta=theta))
+    assert torch.equal(got, K.recon_rope_decode(qd, Ad, Bd, Vd.transpose(1, 2), theta=theta, cta_pair=True))
     logits = ops.decode(entry="xkv_qab_logits", score_mode=_C.SCORE_RECON_ROPE, value_mode=_C.VALUE_DENSE,
-                        q=qd[:, :, 0], k=Ad, k_proj=as_key_proj(Bd, D), logits_only=True, sm_scale=1.0, theta=theta)
+                        q=qd[:, :, 0], k=Ad, k_proj=as_key_proj(Bd, D), logits_only=True, sm_scale=1.0, theta=theta,
+                        extra_flags=_C.FLAG_RECON_PAIR)
     status_ok()
     assert_close(logits, O.qab_rope(q, A, b4(B, b), theta)[:, :, 0], "pair variant logits")

@@ -92,3 +92,64 @@ def test_dense_keys_with_factorized_values(dtype, case):
     assert rc == 0, detail
     close(got, O.gqa_factorized_v_only(q, k, Av, Bv), "v_only two-pass vs oracle")
     assert torch.equal(got, K.group_query_attention_factorized_v_only(qd, kd, Avd, Bvd))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("Rv", [128, 384, 512, 1024])
+def test_rising_logits_force_the_tmem_rescale(dtype, Rv):
+    """Logits that climb along the context, each 64-token tile topping the previous one by about 12 log2
+    units: the second pass's lazily updated reference maximum has to move on nearly every tile, so
+    the in-place rescale of the output rows held in tensor memory runs throughout.  Value ranks 128
+    (one narrow MMA per k-step), 384 (a wide and a narrow one), 512 and 1024 (two column blocks)."""
+    b, H, kvh, L = 2, 32, 8, 1000
+    g = torch.Generator().manual_seed(54)
+    u = torch.nn.functional.normalize(torch.randn(D, generator=g), dim=0)
+    q = (4.0 * u + 0.05 * torch.randn(b, H, 1, D, generator=g)).to(dtype)
+    ramp = (torch.arange(L, dtype=torch.float32) / 64.0 * 23.5)[None, None, :, None]
+    k = (ramp * u + 0.05 * torch.randn(b, kvh, L, D, generator=g)).to(dtype)
+    Av = torch.randn(b, L, Rv, generator=g).to(dtype)
+    Bv = (torch.randn(b, kvh, Rv, D, generator=g) / Rv ** 0.5).to(dtype)
+    qd, kd, Avd, Bvd = (x.to(DEV) for x in (q, k, Av, Bv))
+    s = (k[0, 0].float() @ q[0, 0, 0].float()) * D ** -0.5 * 1.4427              # head 0, log2 units
+    assert s[64:128].max() - s[:64].max() > 8.0 and s[-64:].max() - s[-128:-64].max() > 8.0   # the premise of the test
+    got = K.group_query_attention_factorized_v_only(qd, kd, Avd, Bvd)
+    rc, detail = _C.last_status(torch.device(DEV))
+    assert rc == 0, detail
+    close(got, O.gqa_factorized_v_only(q, k, Av, Bv), f"rising logits, value rank {Rv}")
+    assert torch.equal(got, K.group_query_attention_factorized_v_only(qd, kd, Avd, Bvd))
+
+
+def test_group_with_more_than_128_stacked_heads():
+    """Eight layers of 32 heads share one value latent: 256 stacked head rows, i.e. two head blocks of
+    the second pass, each streaming the latent once."""
+    NL, b, L, R, Rv, G, theta = 8, 2, 700, 64, 256, 4, 500000.0
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(55)
+    H = KVH * G
+    A = torch.randn(b, L, R, generator=g).to(dtype)
+    Av = torch.randn(b, L, Rv, generator=g).to(dtype)
+    qs = [torch.randn(b, H, 1, D, generator=g).to(dtype) for _ in range(NL)]
+    Bs = [(torch.randn(R, KVH * D, generator=g) / R ** 0.5).to(dtype) for _ in range(NL)]
+    Bvs = [(torch.randn(Rv, KVH * D, generator=g) / Rv ** 0.5).to(dtype) for _ in range(NL)]
+    got = K.xkv_group_decode([x.to(DEV) for x in qs], A.to(DEV), [x.to(DEV) for x in Bs], Av.to(DEV),
+                             [x.to(DEV) for x in Bvs], theta=theta)
+    rc, detail = _C.last_status(torch.device(DEV))
+    assert rc == 0, detail
+    want = O.group_decode(qs, A, [b4(x, b) for x in Bs], Av, [b4(x, b) for x in Bvs], theta)
+    for i in range(NL):
+        close(got[i], want[i], f"8-layer group, layer {i}")
+
+
+def test_second_pass_kernels_agree():
+    """The tcgen05 second pass (default) against the mma.sync one (XKV_FLAG_PV_MMA_SYNC) on one call."""
+    b, G, L, R, Rv, theta = 2, 4, 1500, 128, 512, 500000.0
+    g = torch.Generator().manual_seed(56)
+    H = KVH * G
+    q = torch.randn(b, H, 1, D, generator=g).bfloat16().to(DEV)
+    A = torch.randn(b, L, R, generator=g).bfloat16().to(DEV)
+    B = (torch.randn(R, KVH * D, generator=g) / R ** 0.5).bfloat16().to(DEV)
+    Av = torch.randn(b, L, Rv, generator=g).bfloat16().to(DEV)
+    Bv = (torch.randn(Rv, KVH * D, generator=g) / Rv ** 0.5).bfloat16().to(DEV)
+    got = K.recon_rope_decode(q, A, B, Av, Bv, theta=theta)
+    alt = K.recon_rope_decode(q, A, B, Av, Bv, theta=theta, pv_mma_sync=True)
+    close(got, alt.float().cpu(), "tcgen05 vs mma.sync second pass", 4e-3, 3e-3)

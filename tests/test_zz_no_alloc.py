@@ -20,6 +20,7 @@ import pytest
 import torch
 
 from kernel_collections_b200 import _C, ops
+from oracle import xkv_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -46,6 +47,11 @@ def test_builtin_scratch_matches_workspace_path_twice_in_a_row(dtype):
         assert got is out
         assert torch.isfinite(out.float()).all()
         assert torch.equal(out, want), f"seed {seed}: max diff {(out.float() - want.float()).abs().max().item():.3e}"
+        # and against the CPU restatement of the reference's math, within the library's tolerances
+        ref = O.flash_decode_gqa(q.cpu(), k.cpu(), v.cpu(), sm_scale=D ** -0.5)
+        ma, rel = O.error_metrics(out, ref)
+        tol = (1e-4, 1e-4) if dtype == torch.float32 else (2e-2, 1e-2)
+        assert ma <= tol[0] and rel <= tol[1], f"seed {seed}: max_abs={ma:.3e} rel_l2={rel:.3e} against the oracle"
 
 
 def test_builtin_scratch_factorized_rope_path():
