@@ -59,13 +59,15 @@ def find_nvcc() -> str:
     return nvcc
 
 
-def build(force: bool = False, verbose: bool = False, defines=(), lib_path: str = LIB_PATH) -> str:
+def build(force: bool = False, verbose: bool = False, defines=(), lib_path: str = LIB_PATH, overrides=None) -> str:
     """Compile what is stale and link.  `defines` (e.g. ["XKV_TC_PROFILE"]) and another `lib_path`
-    give an instrumented copy of the library next to the regular one (objects are then rebuilt)."""
-    if not force and not defines and not needs_build():
+    give an instrumented copy of the library next to the regular one (its objects live in their own
+    directory); `overrides` maps a source's file name to another path to compile in its place."""
+    overrides = dict(overrides or {})
+    if not force and not defines and not overrides and not needs_build():
         return lib_path
     nvcc = find_nvcc()
-    obj_dir = OBJ_DIR if not defines else OBJ_DIR + "_" + "_".join(defines)
+    obj_dir = OBJ_DIR if not (defines or overrides) else OBJ_DIR + "_" + "_".join(list(defines) + sorted(overrides))
     os.makedirs(obj_dir, exist_ok=True)
     base = [nvcc, *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC] + [f"-D{d}" for d in defines]
     if verbose:
@@ -74,6 +76,7 @@ def build(force: bool = False, verbose: bool = False, defines=(), lib_path: str 
     jobs = []
     for src in sources():
         obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
+        src = overrides.get(os.path.basename(src), src)
         if force or _stale(obj, [src] + hdrs):
             jobs.append((src, obj))
 

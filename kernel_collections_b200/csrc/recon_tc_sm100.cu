@@ -285,6 +285,7 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
   const uint32_t tmem_base = *tmem_slot;
 #ifdef XKV_TC_PROFILE
   const long long t_start_ = clock64();
+  const uint64_t ns_start_ = global_ns();
 #endif
 
   if (warp == 0) {
@@ -693,6 +694,10 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
     atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 9, (unsigned long long)(clock64() - t_start_));
   if (threadIdx.x == 256)   // P.V leader
     atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 10, (unsigned long long)(clock64() - t_start_));
+  if (threadIdx.x == 0) {   // SM cycles and nanoseconds of this CTA: their ratio is the SM clock under load
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 11, (unsigned long long)(clock64() - t_start_));
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 12, (unsigned long long)(global_ns() - ns_start_));
+  }
 #endif
   __syncwarp();
   tc_fence_before();
@@ -786,17 +791,22 @@ static int choose_splits(int rows, int tiles) {
   return best_s;
 }
 
-// Whether the CTA-pair (cta_group::2) variant serves a call: on request (XKV_FLAG_RECON_PAIR), with at
-// least two tiles per row, unless the caller pins single CTAs (XKV_FLAG_RECON_SINGLE_CTA).
-static bool want_pair(const xkv_decode_params& p, int tiles) {
+// Whether the CTA-pair (cta_group::2) variant serves a call.  Two CTAs sharing each MMA halve the bytes
+// of B that every SM pulls through shared memory; that pays once the rank contraction dominates
+// (measured: rank 1024, 4 % faster; rank 512, 10 % slower because the leader then waits for two
+// epilogues per accumulator) and there are enough tiles to fill the 74 pair slots.  The caller can
+// pin either variant with XKV_FLAG_RECON_PAIR / XKV_FLAG_RECON_SINGLE_CTA.
+static bool want_pair(const xkv_decode_params& p, int tiles, int rows) {
   if (p.flags & XKV_FLAG_RECON_SINGLE_CTA) return false;
-  return (p.flags & XKV_FLAG_RECON_PAIR) != 0 && tiles >= 2;
+  if (tiles < 2) return false;
+  if (p.flags & XKV_FLAG_RECON_PAIR) return true;
+  return p.k_rank >= 1024 && (int64_t)rows * tiles >= 8 * (int64_t)device_sm_count();
 }
 
 static bool plan_layers(const xkv_decode_params& p, int num_layers, ReconTcPlan* pl) {
   const int tiles = ceil_div(p.kv_len, TILE_M);
   const int rows = p.batch * num_layers;
-  pl->pair = want_pair(p, tiles) ? 1 : 0;
+  pl->pair = want_pair(p, tiles, rows) ? 1 : 0;
   if (pl->pair) {
     // splits are served by pairs of CTAs: SMs / 2 slots, each slot works through ceil(tiles / 2) rounds
     const int slots = device_sm_count() / 2;

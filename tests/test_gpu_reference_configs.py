@@ -84,7 +84,9 @@ def test_config2_full_size_sampled_rows():
     A, B, q, V = synthetic.recon_rope_inputs(cfg, seed=0)
     qr = O.rope_query(q, cfg.theta, cfg.kv_len)
     Ad, Bd, Vd, qd = A.to(DEV), B.to(DEV), V.to(DEV), qr.to(DEV)
-    assert torch.equal(K.rope_query(q.to(DEV), cfg.theta, cfg.kv_len).cpu(), qr)
+    qk = K.rope_query(q.to(DEV), cfg.theta, cfg.kv_len).cpu()      # the library's own rotation: same up to one ulp
+    assert ((qk.float() - qr.float()).abs() <= 2.0 ** -7 * qr.float().abs().clamp(min=1.0)).all()
+    assert (qk != qr).float().mean().item() < 0.01
     rows = sorted({0, 15, *torch.randint(1, 15, (2,), generator=torch.Generator().manual_seed(2)).tolist()})
     want = {r: O.recon_rope_decode(qr[r:r + 1], A[r:r + 1], b4(B), V[r:r + 1].transpose(1, 2), cfg.theta) for r in rows}
     for pair in (False, True):
