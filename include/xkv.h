@@ -67,6 +67,8 @@ typedef enum xkv_value_mode {
                                      pairs that share each MMA (cross-checks)                */
 #define XKV_FLAG_PV_MMA_SYNC 8u  /* two-pass decode: run the softmax + P.A_v pass on the mma.sync
                                      kernel instead of the tcgen05 one (cross-checks)         */
+#define XKV_FLAG_LATENT_MMA_SYNC 32u /* shared-latent decode (MLA, absorbed caches): keep the mma.sync
+                                     kernel where the tcgen05 CTA-pair kernel would run (cross-checks) */
 #define XKV_FLAG_RECON_PAIR 16u  /* key reconstruction: ask for the CTA-pair variant where the
                                      library would not choose it by itself                    */
 

@@ -17,6 +17,7 @@ XKV_F32, XKV_BF16, XKV_F16 = 0, 1, 2
 SCORE_DENSE, SCORE_LATENT, SCORE_RECON_ROPE, SCORE_RECON = 0, 1, 2, 3
 VALUE_DENSE, VALUE_LATENT = 0, 1
 FLAG_LOGITS_ONLY, FLAG_FORCE_GENERIC, FLAG_RECON_SINGLE_CTA, FLAG_PV_MMA_SYNC, FLAG_RECON_PAIR = 1, 2, 4, 8, 16
+FLAG_LATENT_MMA_SYNC = 32
 
 _DTYPES = {torch.float32: XKV_F32, torch.bfloat16: XKV_BF16, torch.float16: XKV_F16}
 

@@ -76,11 +76,46 @@ def group_query_attention(query, key, value, attn_mask=None, dropout_p=0.0, *, s
     return o.unsqueeze(2)
 
 
-def group_query_attentionv2(query, key, value, attn_mask=None, dropout_p=0.0):
-    """The reference's second formulation of the same op (attention.py:93-182: keys / values
-    broadcast over the group axis instead of folding the group into rows).  It also accepts
-    q_len > 1 there; the decode kernels take the single-step case only."""
-    return group_query_attention(query, key, value, attn_mask, dropout_p)
+def _fold_query_tokens(query, num_kv_heads):
+    """(bsz, H, q_len, D) -> (bsz, H * q_len, 1, D): the q_len tokens of a head become q_len more heads of
+    the same KV head (head h, token t -> row h * q_len + t, which keeps rows of one KV head together), so
+    several query tokens ride on the M dimension of the same MMAs that serve the GQA group."""
+    bsz, H, q_len, D = query.shape
+    return query.reshape(bsz, H * q_len, 1, D)
+
+
+def group_query_attentionv2(query, key, value, attn_mask=None, dropout_p=0.0, *, kv_lens=None):
+    """The reference's second formulation (attention.py:93-182), which also takes q_len > 1 query
+    tokens per sequence (speculative / multi-token decode): every query token attends to the whole
+    cache, and `attn_mask` (additive, broadcastable to (bsz, num_kv_heads, group, q_len, kv_len) or
+    (bsz, num_heads, q_len, kv_len)) carries any causal structure among the new tokens.  Returns
+    (bsz, num_heads, q_len, head_dim).  The query tokens are folded into the head dimension, so they
+    share one pass over K and V; up to 16 rows per KV head (group x q_len) stay on the tensor-core
+    kernel, more run on the portable one."""
+    if query.dim() != 4:
+        raise ValueError(f"query must be (bsz, num_heads, q_len, head_dim); got {tuple(query.shape)}")
+    bsz, H, q_len, D = query.shape
+    if q_len == 1:
+        return group_query_attention(query, key, value, attn_mask, dropout_p, kv_lens=kv_lens)
+    KVH, L = key.shape[1], key.shape[2]
+    if H % KVH != 0:
+        raise AssertionError("num_heads must be multiple of num_kv_heads.")
+    mask = None
+    if attn_mask is not None:
+        if dropout_p != 0.0:
+            raise NotImplementedError("dropout is training-only and not supported by the decode kernels")
+        m = attn_mask
+        if m.dim() == 5:                   # (bsz|1, kvh|1, G|1, q_len|1, L)
+            m = m.expand(m.shape[0], KVH, H // KVH, q_len, m.shape[-1]).reshape(m.shape[0], H * q_len, 1, m.shape[-1])
+        elif m.dim() == 4:                 # (bsz|1, heads|1, q_len|1, L)
+            m = m.expand(m.shape[0], H, q_len, m.shape[-1]).reshape(m.shape[0], H * q_len, 1, m.shape[-1])
+        elif m.dim() == 2:                 # (q_len, L)
+            m = m[None, None].expand(1, H, q_len, m.shape[-1]).reshape(1, H * q_len, 1, m.shape[-1])
+        else:
+            raise ValueError(f"unsupported attn_mask shape {tuple(attn_mask.shape)}")
+        mask = m
+    out = group_query_attention(_fold_query_tokens(query, KVH), key, value, mask, dropout_p, kv_lens=kv_lens)
+    return out.reshape(bsz, H, q_len, D)
 
 
 def group_query_attention_sdpa(query, key, value, attn_mask=None, dropout_p=0.0):

@@ -50,7 +50,7 @@ int validate(const xkv_decode_params* p) {
   return XKV_OK;
 }
 
-enum class Path { kNone, kGeneric, kReconTc, kDenseTc, kLatentTc, kTwoPass };
+enum class Path { kNone, kGeneric, kReconTc, kDenseTc, kLatentTc, kLatentPair, kTwoPass };
 
 struct Plans {
   xkv_decode_params rewritten;   // the call as the chosen kernel sees it (see as_latent)
@@ -83,11 +83,14 @@ Path select(const xkv_decode_params& p, Plans* pl) {
   if (!(p.flags & XKV_FLAG_FORCE_GENERIC)) {
     if (recon_tc_supported(p) && recon_tc_plan(p, &pl->recon)) return Path::kReconTc;
     if (dense_tc_supported(p) && dense_tc_plan(p, &pl->dense)) return Path::kDenseTc;
+    if (latent_pair_supported(p) && latent_pair_plan(p, &pl->latent)) return Path::kLatentPair;
     if (latent_tc_supported(p) && latent_tc_plan(p, &pl->latent)) return Path::kLatentTc;
     xkv_decode_params t;
-    if (as_latent(p, &t) && latent_tc_supported(t) && latent_tc_plan(t, &pl->latent)) {
+    if (as_latent(p, &t)) {
       pl->rewritten = t;
-      return Path::kLatentTc;
+      if (latent_pair_supported(t) && latent_pair_plan(t, &pl->latent)) return Path::kLatentPair;
+      if (latent_tc_supported(t) && latent_tc_plan(t, &pl->latent)) return Path::kLatentTc;
+      pl->rewritten = p;
     }
     if (two_pass_supported(&p, 1) && two_pass_plan(&p, 1, &pl->two_pass)) return Path::kTwoPass;
   }
@@ -134,6 +137,7 @@ const char* xkv_decode_plan(const xkv_decode_params* p) {
     case Path::kReconTc: return "recon_tc";
     case Path::kDenseTc: return "dense_tc";
     case Path::kLatentTc: return "latent_tc";
+    case Path::kLatentPair: return "latent_pair";
     case Path::kTwoPass: return "two_pass";
     case Path::kGeneric: return "generic";
     default: return nullptr;
@@ -147,6 +151,7 @@ size_t xkv_decode_workspace_bytes(const xkv_decode_params* p) {
     case Path::kReconTc: return pl.recon.total_bytes;
     case Path::kDenseTc: return pl.dense.total_bytes;
     case Path::kLatentTc: return pl.latent.total_bytes;
+    case Path::kLatentPair: return pl.latent.total_bytes;
     case Path::kTwoPass: return pl.two_pass.total_bytes;
     case Path::kGeneric: return pl.generic.total_bytes;
     default: return 0;
@@ -168,6 +173,9 @@ int xkv_decode(const xkv_decode_params* p, void* ws, size_t ws_bytes, void* stre
     case Path::kLatentTc:
       if (!ws || ws_bytes < pl.latent.total_bytes) return XKV_ERR_WORKSPACE;
       return latent_tc_decode(pl.rewritten, pl.latent, ws, st);
+    case Path::kLatentPair:
+      if (!ws || ws_bytes < pl.latent.total_bytes) return XKV_ERR_WORKSPACE;
+      return latent_pair_decode(pl.rewritten, pl.latent, ws, st);
     case Path::kTwoPass:
       if (!ws || ws_bytes < pl.two_pass.total_bytes) return XKV_ERR_WORKSPACE;
       return two_pass_decode(p, 1, pl.two_pass, ws, st);

@@ -60,14 +60,17 @@ __device__ __forceinline__ float2 unpack2(uint32_t u, __half) {
   return __half22float2(*reinterpret_cast<__half2*>(&u));
 }
 
-// LO: logits only (first pass of a two-pass decode): K is streamed, V is not, no softmax / P.V.
-template <typename T, bool LO>
+// MODE 0: the whole decode.  MODE 1 (LO): logits only (first pass of a two-pass decode): K is streamed,
+// V is not, no softmax / P.V.  MODE 2 (FL): the scores come as fp32 logits from a first pass (keys that
+// are not dense: factorized without RoPE); only V is streamed.
+template <typename T, int MODE>
 __global__ void __launch_bounds__(NTHREADS, 2)
 dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const Args a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
+  constexpr bool LO = MODE == 1, FL = MODE == 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int row_len = a.kv_lens ? min(max(a.kv_lens[b], 0), a.kv_len) : a.kv_len;   // this row's length
@@ -106,10 +109,12 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
           report(a.status, XKV_ERR_TIMEOUT, 0, tile, kvh, b);
           break;
         }
-        mbar_expect_tx(bar_full(stage), LO ? KV_BYTES : STAGE_BYTES);
+        mbar_expect_tx(bar_full(stage), (LO || FL) ? KV_BYTES : STAGE_BYTES);
         const uint32_t sk = base + stage * STAGE_BYTES;
-        tma_load_4d(sk, &tmK, 0, kvh, tile * TILE, b, bar_full(stage));
-        tma_load_4d(sk + KV_BYTES / 2, &tmK, 64, kvh, tile * TILE, b, bar_full(stage));
+        if (!FL) {
+          tma_load_4d(sk, &tmK, 0, kvh, tile * TILE, b, bar_full(stage));
+          tma_load_4d(sk + KV_BYTES / 2, &tmK, 64, kvh, tile * TILE, b, bar_full(stage));
+        }
         if (!LO) {
           tma_load_4d(sk + KV_BYTES, &tmV, 0, kvh, tile * TILE, b, bar_full(stage));
           tma_load_4d(sk + KV_BYTES + KV_BYTES / 2, &tmV, 64, kvh, tile * TILE, b, bar_full(stage));
@@ -122,7 +127,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     const int cw = warp - 1;                 // tokens cw*16 .. cw*16+15 of every tile
     // Q fragments: A operand (16 heads x 16 dims per k-step), rows >= G are zero
     uint32_t qf[8][4];
-    {
+    if (!FL) {
       const T* qg = static_cast<const T*>(a.q) + (int64_t)b * a.q_sb + (int64_t)(kvh * G) * a.q_sh;
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
@@ -137,6 +142,19 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     uint32_t phase = 0;
     bool alive = true;
     for (int tile = tile_begin; tile < tile_end && alive; ++tile) {
+      float sc[2][4];
+      if (FL) {
+        // this warp's 16 tokens x the 16 padded head rows, in the accumulator layout of S
+        const int tokb = tile * TILE + cw * 16 + 2 * t;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int row = g + (j >> 1) * 8, tok = tokb + n * 8 + (j & 1);
+            sc[n][j] = (row < G && tok < row_len)
+                           ? __ldg(a.logits + (int64_t)b * a.lg_sb + (int64_t)(kvh * G + row) * a.lg_sh + tok) : 0.f;
+          }
+      }
       bool ok = mbar_wait(bar_full(stage), phase, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) report(a.status, XKV_ERR_TIMEOUT, 1, tile, kvh, b);
@@ -145,10 +163,11 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
       }
       const uint32_t sk = base + stage * STAGE_BYTES, sv = sk + KV_BYTES;
       // ---- S = Q . K^T for this warp's 16 tokens: two 8-token n-tiles ---------------------------
-      float sc[2][4];
+      if (!FL) {
 #pragma unroll
-      for (int n = 0; n < 2; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
-      {
+        for (int n = 0; n < 2; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
+      }
+      if (!FL) {
         // ldmatrix (non-transposed): lanes 0-7 / 8-15 address tokens of n-tile 0 (dims k0.., k0+8..),
         // lanes 16-23 / 24-31 the tokens of n-tile 1
         const int mi = lane >> 3, r = lane & 7;
@@ -198,7 +217,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int tok = tok0 + n * 8 + e;
-            v[n * 2 + e] = tok < row_len ? sc[n][rr * 2 + e] * a.scale_log2 : -CUDART_INF_F;
+            v[n * 2 + e] = tok < row_len ? sc[n][rr * 2 + e] * (FL ? 1.4426950408889634f : a.scale_log2) : -CUDART_INF_F;
           }
         float mx = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -310,9 +329,9 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   }
 }
 
-template <typename T, bool LO>
+template <typename T, int MODE>
 int launch(const CUtensorMap& tK, const CUtensorMap& tV, const Args& a, cudaStream_t st) {
-  auto kern = dense_tc_kernel<T, LO>;
+  auto kern = dense_tc_kernel<T, MODE>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
     cudaGetLastError();
     return XKV_ERR_LAUNCH;
@@ -349,6 +368,39 @@ bool dense_tc_supported(const xkv_decode_params& p) {
   if (p.num_kv_heads > 1 && !stride_ok(p.v_sh)) return false;
   if (p.batch > 1 && !stride_ok(p.v_sb)) return false;
   return true;
+}
+
+// Second pass for keys that are not dense: softmax over fp32 logits and P.V with dense values.
+bool dense_tc_values_supported(const xkv_decode_params& p) {
+  if (p.value_mode != XKV_VALUE_DENSE || (p.flags & (XKV_FLAG_LOGITS_ONLY | XKV_FLAG_FORCE_GENERIC))) return false;
+  if (p.dtype != XKV_BF16 && p.dtype != XKV_F16) return false;
+  if (p.logit_cap > 0.f || p.mask || p.num_heads / p.num_kv_heads > 16) return false;
+  if (p.value_dim != D || !aligned16(p.v) || !stride_ok(p.v_sl)) return false;
+  if (p.num_kv_heads > 1 && !stride_ok(p.v_sh)) return false;
+  if (p.batch > 1 && !stride_ok(p.v_sb)) return false;
+  return true;
+}
+
+int dense_tc_values_from_logits(const xkv_decode_params& p, const DenseTcPlan& pl, const LogitsSink& logits, void* ws,
+                                int* status, cudaStream_t st) {
+  char* w = static_cast<char*>(ws);
+  CUtensorMap tV;
+  if (!encode_kv(&tV, p.dtype, p.v, p.num_kv_heads, p.kv_len, p.batch, p.v_sh, p.v_sl, p.v_sb)) return XKV_ERR_NO_DEVICE;
+  Args a;
+  a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = p.num_heads; a.num_kv_heads = p.num_kv_heads;
+  a.group = p.num_heads / p.num_kv_heads;
+  a.num_splits = pl.num_splits; a.tiles_per_row = pl.tiles;
+  a.scale_log2 = 1.4426950408889634f;
+  a.q = nullptr; a.q_sb = a.q_sh = 0;
+  a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
+  a.lse = reinterpret_cast<float*>(w + pl.off_lse);
+  a.status = status;
+  a.logits = logits.ptr; a.lg_sb = logits.sb; a.lg_sh = logits.sh; a.sm_scale = 1.f;
+  a.kv_lens = p.kv_lens;
+  const int rc = p.dtype == XKV_BF16 ? launch<__nv_bfloat16, 2>(tV, tV, a, st) : launch<__half, 2>(tV, tV, a, st);
+  if (rc != XKV_OK) return rc;
+  return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, D, D, nullptr, 1, 0, 0,
+                      0, 0, p.o_sb, p.o_sh, st, 0, 0, p.lse_out, p.lse_sb);
 }
 
 // First pass of the two-pass decode: fp32 logits of dense keys.
@@ -404,9 +456,9 @@ int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& pl, void* ws,
   a.kv_lens = p.kv_lens;
   if (sink) {
     a.logits = sink->ptr; a.lg_sb = sink->sb; a.lg_sh = sink->sh;
-    return p.dtype == XKV_BF16 ? launch<__nv_bfloat16, true>(tK, tV, a, st) : launch<__half, true>(tK, tV, a, st);
+    return p.dtype == XKV_BF16 ? launch<__nv_bfloat16, 1>(tK, tV, a, st) : launch<__half, 1>(tK, tV, a, st);
   }
-  const int rc = p.dtype == XKV_BF16 ? launch<__nv_bfloat16, false>(tK, tV, a, st) : launch<__half, false>(tK, tV, a, st);
+  const int rc = p.dtype == XKV_BF16 ? launch<__nv_bfloat16, 0>(tK, tV, a, st) : launch<__half, 0>(tK, tV, a, st);
   if (rc != XKV_OK) return rc;
   return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, D, D, nullptr, 1, 0, 0,
                       0, 0, p.o_sb, p.o_sh, st, 0, 0, p.lse_out, p.lse_sb);

@@ -1,0 +1,583 @@
+// Shared-latent decode (MLA, absorbed factorized caches) on tcgen05, two CTAs per (KV split, head
+// block, batch row).
+//
+// Up to 128 query heads sit on the M dimension of every MMA.  The output rows O[128 x Rv] (fp32)
+// alone would fill the 512 tensor-memory columns of an SM, and the resident queries Q[128 x Dk] most
+// of its shared memory, so a CLUSTER OF TWO CTAs shares each 48-token tile:
+//   * CTA r owns half of the value columns (O[128 x Rv/2] stays in its tensor memory for the whole
+//     split) and half of the score contraction: it keeps the matching 64-wide blocks of Q resident,
+//     streams only those blocks of the latent rows (each latent byte is fetched by exactly one of the
+//     two CTAs, so the pair reads the cache once), and forms S_r = Q_r . K_r^T on the tensor core;
+//   * the two partial score tiles are exchanged through distributed shared memory (plain 128-bit
+//     stores into the peer's buffer + an mbarrier arrive, no multicast) and added; both CTAs then
+//     hold the same S, run the same softmax (one thread per head row, lazily updated reference
+//     maximum as in the two-pass value kernel) and multiply their own value columns: O_r += P . V_r.
+// Warps: 0 TMA producer (3-stage ring of whole tiles), 1 MMA issuer (S of tile i+1 is issued before
+// P.V of tile i: two score buffers in tensor memory), 2 tensor-memory allocation, 4-7 softmax.
+// Every wait is bounded; on expiry the CTA raises its abort flag, reports where it gave up, drains,
+// frees its tensor memory and leaves (the peer's waits then run out the same way).
+#include "sm100_common.cuh"
+
+namespace xkv {
+using namespace sm100;
+namespace {
+
+constexpr int T = 48;                        // tokens per tile
+constexpr int MAXB = 5;                      // 64-column blocks per CTA and tile
+constexpr int BLK = T * 128;                 // bytes of one [48 tokens x 64 columns] block
+constexpr int STAGES = 3;
+constexpr int QBLK = 128 * 128;              // bytes of one [128 heads x 64 columns] query block
+constexpr int NTHREADS = 256;
+constexpr int OFF_Q = 0;
+constexpr int OFF_RING = OFF_Q + MAXB * QBLK;                 // 81920
+constexpr int OFF_P = OFF_RING + STAGES * MAXB * BLK;         // 174080
+constexpr int P_BYTES = 128 * 128;                            // 128 head rows x 64 token slots (48 used)
+constexpr int OFF_X = OFF_P + P_BYTES;                        // 190464: partial scores from the peer
+constexpr int X_BYTES = (T / 4) * 128 * 16;                   // [T/4][128 rows][4 floats] = 24576
+constexpr int OFF_BAR = OFF_X + X_BYTES;                      // 215040
+constexpr int OFF_MISC = OFF_BAR + 16 * 8;
+constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;
+static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
+static_assert(OFF_RING % 1024 == 0 && BLK % 1024 == 0 && OFF_P % 1024 == 0, "swizzled blocks need 1024-byte alignment");
+constexpr float RESCALE_THRESHOLD = 8.f;
+constexpr uint32_t S_COL0 = 256;             // tensor-memory columns: O in 0..255, two score buffers at 256 / 320
+
+// The 64-column blocks one CTA of the pair works on.  Blocks [0, nv) are its own value columns (in
+// alias mode they are score blocks too); blocks with score[i] set take part in S.
+struct BlockList {
+  int n, nv;
+  int col[MAXB];        // column (elements) inside the tensor the block is loaded from
+  int src[MAXB];        // 0: key latent, 1: decoupled RoPE key part, 2: value latent
+  int qcol[MAXB];       // matching column of the effective query, or -1 when the block is values only
+};
+
+struct Args {
+  int batch, kv_len, num_heads, dk;
+  int num_splits, tiles_per_row;
+  float scale_log2;
+  const void* qeff;                       // [batch][H][dk], working dtype
+  float* partial_o;                       // [batch][H][splits][rv]
+  float* lse;                             // [batch][H][splits]
+  int rv;
+  int* status;
+  const int32_t* kv_lens;
+  BlockList bl[2];
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_remote_v4(uint32_t cluster_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+// Bounded wait whose acquire covers writes made by the other CTA of the cluster.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const uint64_t t0 = global_ns();
+  for (uint32_t it = 0; it < MAX_POLLS; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 31u) == 31u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > WAIT_LIMIT_NS) break;
+      __nanosleep(32);
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+template <typename T_>
+__global__ void __launch_bounds__(NTHREADS, 1)
+latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmKt,
+                   const __grid_constant__ CUtensorMap tmV, const Args a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank(), peer = rank ^ 1u;
+  const int split = blockIdx.x >> 1, hb = blockIdx.y, b = blockIdx.z;
+  const BlockList& bl = a.bl[rank];
+  const int h0 = hb * 128;
+  const int row_len = a.kv_lens ? min(max(a.kv_lens[b], 0), a.kv_len) : a.kv_len;
+  const int row_tiles = a.kv_lens ? (row_len + T - 1) / T : a.tiles_per_row;
+  const int tile_begin = (int)(((int64_t)split * row_tiles) / a.num_splits);
+  const int tile_end = (int)(((int64_t)(split + 1) * row_tiles) / a.num_splits);
+  const int ntiles = tile_end - tile_begin;
+  const int nvc = bl.nv * 64;                               // value columns of this CTA
+  const int col_out = (int)rank * (a.rv / 2);               // where they sit in the output row
+  const uint32_t stage_bytes = (uint32_t)bl.n * BLK;
+
+  const uint32_t bar0 = base + OFF_BAR;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+  auto bar_sfull = [&](int i) { return bar0 + 8u * (6 + i); };
+  auto bar_sempty = [&](int i) { return bar0 + 8u * (8 + i); };
+  const uint32_t bar_pfull = bar0 + 8u * 10, bar_pempty = bar0 + 8u * 11, bar_odone = bar0 + 8u * 12;
+  const uint32_t bar_xfull = bar0 + 8u * 13;    // the peer's partial scores have landed in my buffer
+  const uint32_t bar_xfree = bar0 + 8u * 14;    // the peer has read its buffer: I may write the next tile into it
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + OFF_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 4);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_sfull(i), 1); mbar_init(bar_sempty(i), 128); }
+    mbar_init(bar_pfull, 128);
+    mbar_init(bar_pempty, 1);
+    mbar_init(bar_odone, 1);
+    mbar_init(bar_xfull, 128);
+    mbar_init(bar_xfree, 128);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + OFF_MISC), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // resident queries: the score blocks of this CTA, rows past num_heads are zero
+  {
+    const T_* qg = static_cast<const T_*>(a.qeff) + ((int64_t)b * a.num_heads + h0) * a.dk;
+    int qi = 0;
+    for (int i = 0; i < bl.n; ++i) {
+      if (bl.qcol[i] < 0) continue;
+      for (int c = threadIdx.x; c < 128 * 8; c += NTHREADS) {
+        const int r = c >> 3, ch = c & 7;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (h0 + r < a.num_heads) v = *reinterpret_cast<const uint4*>(qg + (int64_t)r * a.dk + bl.qcol[i] + ch * 8);
+        *reinterpret_cast<uint4*>(sm + OFF_Q + qi * QBLK + r * 128 + ((ch ^ (r & 7)) << 4)) = v;
+      }
+      ++qi;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // the peer's barriers exist before anything is signalled across CTAs
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // =========================== producer: whole tiles of this CTA's blocks ========================
+    if (lane == 0) {
+      for (int i = 0; i < ntiles; ++i) {
+        const int stage = i % STAGES;
+        if (!mbar_wait(bar_empty(stage), ((uint32_t)(i / STAGES) & 1u) ^ 1u, abort_flag)) {
+          report(a.status, XKV_ERR_TIMEOUT, 30, tile_begin + i, (int)rank, b);
+          break;
+        }
+        mbar_expect_tx(bar_full(stage), stage_bytes);
+        const uint32_t ss = base + OFF_RING + stage * (MAXB * BLK);
+        const int tok = (tile_begin + i) * T;
+        for (int k = 0; k < bl.n; ++k) {
+          const CUtensorMap* m = bl.src[k] == 0 ? &tmK : (bl.src[k] == 1 ? &tmKt : &tmV);
+          tma_load_3d(ss + k * BLK, m, bl.col[k], tok, b, bar_full(stage));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================================================
+    if (lane == 0 && ntiles > 0) {
+      const uint32_t kfmt = TypeTraits<T_>::kFmt;
+      // S = Q . K^T: both operands K-major, N = 48 tokens; O += P . V: A = P K-major, B = values MN-major
+      const uint32_t idesc_s = (1u << 4) | (kfmt << 7) | (kfmt << 10) | (((uint32_t)T >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t idesc_o = (1u << 4) | (kfmt << 7) | (kfmt << 10) | (1u << 16) | (((uint32_t)nvc >> 3) << 17) |
+                               ((128u >> 4) << 24);
+      auto issue_scores = [&](int i) -> bool {
+        const int stage = i % STAGES, sb = i & 1;
+        if (i >= 2 && !mbar_wait(bar_sempty(sb), ((uint32_t)((i - 2) >> 1) & 1u), abort_flag)) return false;
+        if (!mbar_wait(bar_full(stage), (uint32_t)(i / STAGES) & 1u, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t ss = base + OFF_RING + stage * (MAXB * BLK);
+        const uint32_t tacc = tmem_base + S_COL0 + (uint32_t)sb * 64u;
+        int qi = 0;
+        bool first = true;
+        for (int k = 0; k < bl.n; ++k) {
+          if (bl.qcol[k] < 0) continue;
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const uint64_t da = smem_desc(base + OFF_Q + qi * QBLK + k4 * 32, 16, 1024);
+            const uint64_t db = smem_desc(ss + k * BLK + k4 * 32, 16, 1024);
+            tc_mma(tacc, da, db, idesc_s, first ? 0u : 1u);
+            first = false;
+          }
+          ++qi;
+        }
+        tc_commit(bar_sfull(sb));
+        return true;
+      };
+      bool ok = issue_scores(0);
+      for (int i = 0; ok && i < ntiles; ++i) {
+        if (i + 1 < ntiles) ok = issue_scores(i + 1);
+        if (!ok) break;
+        if (!mbar_wait(bar_pfull, (uint32_t)i & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t ss = base + OFF_RING + (i % STAGES) * (MAXB * BLK);
+#pragma unroll
+        for (int k4 = 0; k4 < T / 16; ++k4) {
+          const uint64_t da = smem_desc(base + OFF_P + k4 * 32, 16, 1024);
+          const uint64_t db = smem_desc(ss + k4 * 2048, BLK, 1024);
+          tc_mma(tmem_base, da, db, idesc_o, (i == 0 && k4 == 0) ? 0u : 1u);
+        }
+        tc_commit(bar_empty(i % STAGES));      // the tile's blocks and ...
+        tc_commit(bar_pempty);                 // ... the P buffer are free once these MMAs have run
+      }
+      if (ok) tc_commit(bar_odone);
+      else report(a.status, XKV_ERR_TIMEOUT, 31, tile_begin, (int)rank, b);
+    }
+  } else if (warp >= 4) {
+    // =========================== softmax: one thread per head row =====================================
+    const int r = threadIdx.x - 128;
+    const int h = h0 + r;
+    const bool live = h < a.num_heads;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t x_local = base + OFF_X + (uint32_t)r * 16u;            // [g][row][4]: + g * 2048
+    const uint32_t x_peer = map_to_cta(x_local, peer);
+    const uint32_t xfull_peer = map_to_cta(bar_xfull, peer), xfree_peer = map_to_cta(bar_xfree, peer);
+    float m_ref = -CUDART_INF_F, l_sum = 0.f;
+    bool alive = true;
+    for (int i = 0; i < ntiles && alive; ++i) {
+      const int sb = i & 1;
+      // ---- own partial scores out of tensor memory ---------------------------------------------------
+      if (!mbar_wait(bar_sfull(sb), (uint32_t)(i >> 1) & 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 32, tile_begin + i, (int)rank, b);
+      tc_fence_after();
+      float s[T];
+      {
+        uint32_t v[16];
+#pragma unroll
+        for (int c = 0; c < T; c += 16) {
+          tmem_ld16(lane_addr + S_COL0 + (uint32_t)sb * 64u + c, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) s[c + e] = __uint_as_float(v[e]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_sempty(sb));
+      // ---- exchange with the peer: my partial into its buffer, its partial out of mine ------------------
+      if (i > 0 && !mbar_wait_cluster(bar_xfree, (uint32_t)(i - 1) & 1u, abort_flag))
+        report(a.status, XKV_ERR_TIMEOUT, 33, tile_begin + i, (int)rank, b);
+#pragma unroll
+      for (int g4 = 0; g4 < T / 4; ++g4)
+        st_remote_v4(x_peer + g4 * 2048, s[4 * g4], s[4 * g4 + 1], s[4 * g4 + 2], s[4 * g4 + 3]);
+      mbar_arrive_remote(xfull_peer);
+      if (!mbar_wait_cluster(bar_xfull, (uint32_t)i & 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 34, tile_begin + i, (int)rank, b);
+      const int t0 = (tile_begin + i) * T;
+#pragma unroll
+      for (int g4 = 0; g4 < T / 4; ++g4) {
+        float4 o;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(o.x), "=f"(o.y), "=f"(o.z), "=f"(o.w) : "r"(x_local + g4 * 2048));
+        // (a + b == b + a exactly: both CTAs end up with the same bits)
+        s[4 * g4] = (s[4 * g4] + o.x) * a.scale_log2;
+        s[4 * g4 + 1] = (s[4 * g4 + 1] + o.y) * a.scale_log2;
+        s[4 * g4 + 2] = (s[4 * g4 + 2] + o.z) * a.scale_log2;
+        s[4 * g4 + 3] = (s[4 * g4 + 3] + o.w) * a.scale_log2;
+      }
+      mbar_arrive_remote(xfree_peer);
+      float tmax = -CUDART_INF_F;
+#pragma unroll
+      for (int e = 0; e < T; ++e) {
+        if (t0 + e >= row_len || !live) s[e] = -CUDART_INF_F;
+        tmax = fmaxf(tmax, s[e]);
+      }
+      // ---- lazily updated reference maximum; all 128 rows agree on whether to rescale -------------------
+      const bool move = tmax > m_ref + RESCALE_THRESHOLD || (m_ref == -CUDART_INF_F && tmax > -CUDART_INF_F);
+      uint32_t anym, anya;
+      {
+        const uint32_t mine = (move ? 1u : 0u) | (*abort_flag ? 2u : 0u);
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.u32 p, %2, 0;\n\t"
+            "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
+            "selp.u32 %0, 1, 0, q;\n\t"
+            "setp.ne.u32 p, %3, 0;\n\t"
+            "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
+            "selp.u32 %1, 1, 0, q;\n\t}"
+            : "=r"(anym), "=r"(anya)
+            : "r"(mine & 1u), "r"(mine & 2u)
+            : "memory");
+      }
+      if (anya) { alive = false; break; }
+      // the single P buffer (and, for a rescale, the output rows) are free once P.V of the previous tile has run
+      if (i > 0 && !mbar_wait(bar_pempty, (uint32_t)(i - 1) & 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 35, tile_begin + i, (int)rank, b);
+      if (anym) {
+        const float m_new = move ? tmax : m_ref;
+        const float alpha = (m_ref == -CUDART_INF_F) ? 0.f : exp2f(m_ref - m_new);
+        if (i > 0) {
+          tc_fence_after();
+          for (int c = 0; c < nvc; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(lane_addr + c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+            tmem_st32(lane_addr + c, v);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+        }
+        l_sum *= alpha;
+        m_ref = m_new;
+      }
+      // ---- P row -> shared memory (K-major, 128-byte swizzle), row sum of the rounded values ------------
+      const float mref = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+      uint8_t* prow = sm + OFF_P + r * 128;
+#pragma unroll
+      for (int c8 = 0; c8 < T / 8; ++c8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = exp2f(s[c8 * 8 + 2 * e] - mref), p1 = exp2f(s[c8 * 8 + 2 * e + 1] - mref);
+          T_ q0 = TypeTraits<T_>::from_f(p0), q1 = TypeTraits<T_>::from_f(p1);
+          l_sum += TypeTraits<T_>::to_f(q0) + TypeTraits<T_>::to_f(q1);
+          pk[e] = (uint32_t)(*reinterpret_cast<uint16_t*>(&q0)) | ((uint32_t)(*reinterpret_cast<uint16_t*>(&q1)) << 16);
+        }
+        *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      // ragged batch, last tile of the row: value rows past the row's own length may hold anything (NaN
+      // included, and 0 * NaN is NaN): zero them before the MMAs read the tile
+      if (a.kv_lens != nullptr && t0 + T > row_len) {
+        const int stage = i % STAGES;
+        if (!mbar_wait(bar_full(stage), (uint32_t)(i / STAGES) & 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 36, tile_begin + i, (int)rank, b);
+        const int first = max(row_len - t0, 0), per_row = bl.nv * 8;
+        for (int idx = r; idx < (T - first) * per_row; idx += 128) {
+          const int row = first + idx / per_row, rem = idx % per_row;
+          *reinterpret_cast<uint4*>(sm + OFF_RING + stage * (MAXB * BLK) + (rem >> 3) * BLK + row * 128 + (rem & 7) * 16) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+      mbar_arrive(bar_pfull);
+    }
+    // ---- output: O row / l, log-sum-exp ---------------------------------------------------------------
+    if (alive && ntiles > 0) {
+      if (!mbar_wait(bar_odone, 0, abort_flag)) { report(a.status, XKV_ERR_TIMEOUT, 37, tile_end, (int)rank, b); alive = false; }
+      tc_fence_after();
+    }
+    if (alive && !*abort_flag) {
+      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      float* po = a.partial_o + (((int64_t)b * a.num_heads + (live ? h : 0)) * a.num_splits + split) * a.rv + col_out;
+      for (int c = 0; c < nvc; c += 32) {
+        uint32_t v[32];
+        if (ntiles > 0) {                    // (warp-wide tensor-memory load: rows past the last head take part)
+          tmem_ld32(lane_addr + c, v);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = 0u;
+        }
+        if (live) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            *reinterpret_cast<float4*>(po + c + e) =
+                make_float4(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv,
+                            __uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+        }
+      }
+      if (live && rank == 0)
+        a.lse[((int64_t)b * a.num_heads + h) * a.num_splits + split] =
+            l_sum > 0.f ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -CUDART_INF_F;
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  // neither CTA leaves while the other may still store into its shared memory or signal its barriers
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+bool encode_rows(CUtensorMap* m, int dtype, const void* ptr, int width, int L, int batch, int64_t sl, int64_t sb) {
+  const cuuint64_t dims[3] = {(cuuint64_t)width, (cuuint64_t)L, (cuuint64_t)batch};
+  const int64_t sbb = batch > 1 ? sb : (int64_t)L * sl;
+  const cuuint64_t strides[2] = {(cuuint64_t)sl * 2, (cuuint64_t)sbb * 2};
+  const cuuint32_t box[3] = {64, T, 1};
+  return encode_tiled_16bit(m, dtype, 3, ptr, dims, strides, box);
+}
+
+bool aliased(const xkv_decode_params& p) {
+  return p.v == p.k && p.v_sl == p.k_sl && p.v_sb == p.k_sb && p.v_rank <= p.k_rank;
+}
+
+// Split the 64-column blocks of a call between the two CTAs: each takes half of the value columns
+// (and, in alias mode, scores those same blocks); the remaining score blocks are dealt out so that
+// the two lists are as even as possible.  Returns false when a CTA would need more than MAXB blocks.
+bool make_lists(const xkv_decode_params& p, BlockList out[2]) {
+  const bool al = aliased(p);
+  const int nvb = p.v_rank / 64, kb = p.k_rank / 64, tb = p.tail_dim / 64;
+  for (int r = 0; r < 2; ++r) {
+    BlockList& l = out[r];
+    l.n = 0;
+    l.nv = nvb / 2;
+    for (int i = 0; i < l.nv; ++i) {
+      const int blk = r * l.nv + i;
+      l.col[l.n] = blk * 64;
+      l.src[l.n] = al ? 0 : 2;
+      l.qcol[l.n] = al ? blk * 64 : -1;
+      ++l.n;
+    }
+  }
+  // score blocks not covered above: all key blocks (separate value latent) or the key blocks past the
+  // value columns (alias), then the decoupled RoPE blocks
+  int turn = 0;
+  for (int blk = al ? nvb : 0; blk < kb + tb; ++blk) {
+    BlockList& l = out[out[0].n <= out[1].n ? 0 : 1];
+    (void)turn;
+    if (l.n >= MAXB) return false;
+    if (blk < kb) { l.col[l.n] = blk * 64; l.src[l.n] = 0; }
+    else { l.col[l.n] = (blk - kb) * 64; l.src[l.n] = 1; }
+    l.qcol[l.n] = blk * 64;
+    ++l.n;
+  }
+  // each CTA must score at least one block (its score buffer is exchanged every tile)
+  for (int r = 0; r < 2; ++r) {
+    int ns = 0;
+    for (int i = 0; i < out[r].n; ++i) ns += out[r].qcol[i] >= 0;
+    if (ns == 0 || out[r].n > MAXB) return false;
+  }
+  return true;
+}
+
+template <typename T_>
+int launch(const CUtensorMap& tK, const CUtensorMap& tKt, const CUtensorMap& tV, const Args& a, int head_blocks,
+           cudaStream_t st) {
+  auto kern = latent_pair_kernel<T_>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
+    cudaGetLastError();
+    return XKV_ERR_LAUNCH;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.num_splits * 2, head_blocks, a.batch);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, tK, tKt, tV, a) != cudaSuccess) {
+    cudaGetLastError();
+    return XKV_ERR_LAUNCH;
+  }
+  return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
+}
+
+}  // namespace
+
+bool latent_pair_supported(const xkv_decode_params& p) {
+  if (p.score_mode != XKV_SCORE_LATENT || p.value_mode != XKV_VALUE_LATENT) return false;
+  if (p.flags & (XKV_FLAG_LOGITS_ONLY | XKV_FLAG_FORCE_GENERIC | XKV_FLAG_LATENT_MMA_SYNC)) return false;
+  if (p.dtype != XKV_BF16 && p.dtype != XKV_F16) return false;
+  if (p.logit_cap > 0.f || p.mask) return false;
+  if (p.num_heads < 64) return false;      // fewer heads leave most MMA rows empty: the mma.sync kernel serves them
+  if (p.k_rank % 64 != 0 || p.tail_dim % 64 != 0 || p.v_rank % 128 != 0 || p.v_rank > 512) return false;
+  if (!aligned16(p.k) || !aligned16(p.v) || !stride_ok(p.k_sl) || !stride_ok(p.v_sl)) return false;
+  if (p.batch > 1 && (!stride_ok(p.k_sb) || !stride_ok(p.v_sb))) return false;
+  if (p.tail_dim > 0 && (!aligned16(p.k_tail) || !stride_ok(p.kt_sl) || (p.batch > 1 && !stride_ok(p.kt_sb)))) return false;
+  BlockList bl[2];
+  return make_lists(p, bl);
+}
+
+bool latent_pair_plan(const xkv_decode_params& p, LatentTcPlan* pl) {
+  const int head_blocks = ceil_div(p.num_heads, 128);
+  const int tiles = ceil_div(p.kv_len, T);
+  const int rows = p.batch * head_blocks;
+  const int slots = device_sm_count() / 2;      // clusters of two CTAs
+  int best_s = 1;
+  int64_t best_cost = -1;
+  const int max_s = tiles < 64 ? tiles : 64;
+  for (int s = 1; s <= max_s; ++s) {
+    const int64_t waves = ceil_div(rows * s, slots);
+    const int64_t cost = waves * (ceil_div(tiles, s) + 6);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = s; }
+  }
+  pl->heads_per_cta = 128;
+  pl->stages = STAGES;
+  pl->smem_bytes = SMEM_BYTES;
+  pl->num_splits = best_s;
+  pl->tiles = tiles;
+  const int dk = p.k_rank + p.tail_dim;
+  size_t off = 256;
+  pl->off_qeff = off;
+  off += align_up((size_t)p.batch * p.num_heads * dk * 2, 256);
+  pl->off_partial = off;
+  off += align_up((size_t)p.batch * p.num_heads * best_s * p.v_rank * sizeof(float), 256);
+  pl->off_lse = off;
+  off += align_up((size_t)p.batch * p.num_heads * best_s * sizeof(float), 256);
+  pl->total_bytes = off;
+  return true;
+}
+
+int latent_pair_decode(const xkv_decode_params& p, const LatentTcPlan& pl, void* ws, cudaStream_t st) {
+  char* w = static_cast<char*>(ws);
+  const int dk = p.k_rank + p.tail_dim;
+  CUtensorMap tK, tKt, tV;
+  if (!encode_rows(&tK, p.dtype, p.k, p.k_rank, p.kv_len, p.batch, p.k_sl, p.k_sb)) return XKV_ERR_NO_DEVICE;
+  if (p.tail_dim > 0) {
+    if (!encode_rows(&tKt, p.dtype, p.k_tail, p.tail_dim, p.kv_len, p.batch, p.kt_sl, p.kt_sb)) return XKV_ERR_NO_DEVICE;
+  } else {
+    tKt = tK;
+  }
+  if (!aliased(p)) {
+    if (!encode_rows(&tV, p.dtype, p.v, p.v_rank, p.kv_len, p.batch, p.v_sl, p.v_sb)) return XKV_ERR_NO_DEVICE;
+  } else {
+    tV = tK;
+  }
+  int* status = reinterpret_cast<int*>(w);
+  sm100::clear_status_kernel<<<1, 64, 0, st>>>(status);
+  void* qeff = w + pl.off_qeff;
+  int rc = launch_absorb_query_lowp(p, qeff, dk, st);
+  if (rc != XKV_OK) return rc;
+  Args a;
+  a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = p.num_heads; a.dk = dk;
+  a.num_splits = pl.num_splits; a.tiles_per_row = pl.tiles;
+  a.scale_log2 = p.sm_scale * 1.4426950408889634f;
+  a.qeff = qeff;
+  a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
+  a.lse = reinterpret_cast<float*>(w + pl.off_lse);
+  a.rv = p.v_rank;
+  a.status = status;
+  a.kv_lens = p.kv_lens;
+  if (!make_lists(p, a.bl)) return XKV_ERR_UNSUPPORTED;
+  const int head_blocks = ceil_div(p.num_heads, 128);
+  rc = p.dtype == XKV_BF16 ? launch<__nv_bfloat16>(tK, tKt, tV, a, head_blocks, st)
+                           : launch<__half>(tK, tKt, tV, a, head_blocks, st);
+  if (rc != XKV_OK) return rc;
+  return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, p.v_rank, p.value_dim,
+                      p.v_proj, p.v_proj ? p.v_proj_heads : 1, p.vp_sb, p.vp_sh, p.vp_sr, p.vp_sd, p.o_sb, p.o_sh, st, 0, 0,
+                      p.lse_out, p.lse_sb);
+}
+
+}  // namespace xkv

@@ -31,9 +31,10 @@ struct Args {
   const void* qeff;                     // [batch][H][dk], working dtype
   const float* logits;                  // FL mode: fp32 logits [b * lg_sb + h * lg_sh + token] from a first pass
   int64_t lg_sb, lg_sh;
-  void* logits_out;                     // logits-only mode: lo_scale * q_eff.k in the working dtype, no softmax / P.V
-  int64_t lo_sb, lo_sh;
+  void* logits_out;                     // logits-only mode: lo_scale * q_eff.k, no softmax / P.V; in the working
+  int64_t lo_sb, lo_sh;                 // dtype, or fp32 (lo_f32) when they feed a second pass
   float lo_scale;
+  int lo_f32;
   float* partial_o;                     // [batch][H][splits][rv]
   float* lse;                           // [batch][H][splits]
   int* status;
@@ -254,9 +255,11 @@ latent_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int h = h0 + mt_w * 16 + g + (i >> 1) * 8, tk = tok + (i & 1);
-            if (h < a.num_heads && tk < row_len)
-              static_cast<T*>(a.logits_out)[(int64_t)b * a.lo_sb + (int64_t)h * a.lo_sh + tk] =
-                  TypeTraits<T>::from_f(sc[u][i] * a.lo_scale);
+            if (h < a.num_heads && tk < row_len) {
+              const int64_t off = (int64_t)b * a.lo_sb + (int64_t)h * a.lo_sh + tk;
+              if (a.lo_f32) static_cast<float*>(a.logits_out)[off] = sc[u][i] * a.lo_scale;
+              else static_cast<T*>(a.logits_out)[off] = TypeTraits<T>::from_f(sc[u][i] * a.lo_scale);
+            }
           }
         }
         release_stage_counted(tile, stage);
@@ -494,6 +497,16 @@ int dispatch(int hb, int nt, const CUtensorMap& tK, const CUtensorMap& tKt, cons
 
 }  // namespace
 
+int launch_absorb_query_lowp(const xkv_decode_params& p, void* qeff, int dk, cudaStream_t st) {
+  if (p.dtype == XKV_BF16)
+    absorb_query_lowp_kernel<__nv_bfloat16><<<dim3(p.num_heads, p.batch), 128, p.head_dim * sizeof(float), st>>>(
+        p, static_cast<__nv_bfloat16*>(qeff), dk);
+  else
+    absorb_query_lowp_kernel<__half><<<dim3(p.num_heads, p.batch), 128, p.head_dim * sizeof(float), st>>>(
+        p, static_cast<__half*>(qeff), dk);
+  return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
+}
+
 // A logits-only call is planned as if the values aliased the key latent: nothing but keys is streamed.
 static xkv_decode_params normalized(const xkv_decode_params& p) {
   xkv_decode_params t = p;
@@ -562,7 +575,8 @@ bool latent_tc_plan(const xkv_decode_params& pin, LatentTcPlan* pl) {
   return true;
 }
 
-int latent_tc_decode(const xkv_decode_params& pin, const LatentTcPlan& pl, void* ws, cudaStream_t st) {
+int latent_tc_decode(const xkv_decode_params& pin, const LatentTcPlan& pl, void* ws, cudaStream_t st,
+                     const LogitsSink* sink) {
   const xkv_decode_params p = normalized(pin);
   const bool lo = (pin.flags & XKV_FLAG_LOGITS_ONLY) != 0;
   char* w = static_cast<char*>(ws);
@@ -583,12 +597,7 @@ int latent_tc_decode(const xkv_decode_params& pin, const LatentTcPlan& pl, void*
   int* status = reinterpret_cast<int*>(w);
   clear_status_kernel<<<1, 64, 0, st>>>(status);
   void* qeff = w + pl.off_qeff;
-  if (p.dtype == XKV_BF16)
-    absorb_query_lowp_kernel<__nv_bfloat16><<<dim3(p.num_heads, p.batch), 128, p.head_dim * sizeof(float), st>>>(
-        p, static_cast<__nv_bfloat16*>(qeff), dk);
-  else
-    absorb_query_lowp_kernel<__half><<<dim3(p.num_heads, p.batch), 128, p.head_dim * sizeof(float), st>>>(
-        p, static_cast<__half*>(qeff), dk);
+  if (launch_absorb_query_lowp(p, qeff, dk, st) != XKV_OK) return XKV_ERR_LAUNCH;
   Args a;
   a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = p.num_heads;
   a.dk = dk; a.rk = p.k_rank; a.rv = p.v_rank; a.alias_v = alias ? 1 : 0;
@@ -603,6 +612,10 @@ int latent_tc_decode(const xkv_decode_params& pin, const LatentTcPlan& pl, void*
   const int nt = p.v_rank / 64;
   a.logits = nullptr; a.lg_sb = a.lg_sh = 0;
   a.logits_out = lo ? pin.logits : nullptr; a.lo_sb = pin.lg_sb; a.lo_sh = pin.lg_sh; a.lo_scale = pin.sm_scale;
+  a.lo_f32 = 0;
+  if (sink) {   // first pass of a two-pass decode: fp32 logits into the caller's buffer (pin carries XKV_FLAG_LOGITS_ONLY)
+    a.logits_out = sink->ptr; a.lo_sb = sink->sb; a.lo_sh = sink->sh; a.lo_f32 = 1;
+  }
   const int rc = p.dtype == XKV_BF16
                      ? dispatch<__nv_bfloat16, false>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st)
                      : dispatch<__half, false>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st);
@@ -669,7 +682,7 @@ int latent_pv_run(const xkv_decode_params& p, int heads, const LatentTcPlan& pl,
   a.num_splits = pl.num_splits; a.tiles_per_row = pl.tiles; a.stages = pl.stages;
   a.scale_log2 = 1.4426950408889634f;
   a.qeff = nullptr;
-  a.logits_out = nullptr; a.lo_sb = a.lo_sh = 0; a.lo_scale = 1.f;
+  a.logits_out = nullptr; a.lo_sb = a.lo_sh = 0; a.lo_scale = 1.f; a.lo_f32 = 0;
   a.logits = logits; a.lg_sb = (int64_t)heads * p.kv_len; a.lg_sh = p.kv_len;
   a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
   a.lse = reinterpret_cast<float*>(w + pl.off_lse);

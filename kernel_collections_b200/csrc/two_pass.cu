@@ -22,10 +22,26 @@ bool same_values(const xkv_decode_params& a, const xkv_decode_params& b) {
 }
 }  // namespace
 
+// Factorized keys without RoPE in front of dense values (the reference's `k_only` fused kernel):
+// logits from the shared-latent kernel (absorbed order, the latent is streamed once), then softmax
+// and P.V on the dense-value kernel.
+static xkv_decode_params key_logits_call(const xkv_decode_params& p) {
+  xkv_decode_params t = p;
+  t.flags |= XKV_FLAG_LOGITS_ONLY;
+  t.lg_sb = (int64_t)p.num_heads * p.kv_len;
+  t.lg_sh = p.kv_len;
+  return t;
+}
+static bool dense_values_supported(const xkv_decode_params& p) {
+  if (p.score_mode != XKV_SCORE_LATENT || p.value_mode != XKV_VALUE_DENSE || p.tail_dim != 0 || !p.k_proj) return false;
+  return dense_tc_values_supported(p) && latent_tc_supported(key_logits_call(p));
+}
+
 bool two_pass_supported(const xkv_decode_params* layers, int n) {
   if (n < 1 || n > 8) return false;
   const xkv_decode_params& p = layers[0];
   if (p.flags & (XKV_FLAG_FORCE_GENERIC | XKV_FLAG_LOGITS_ONLY)) return false;
+  if (n == 1 && dense_values_supported(p)) return true;
   if (!latent_pv_supported(p)) return false;
   for (int i = 0; i < n; ++i) {
     if (!same_values(p, layers[i]) || layers[i].score_mode != p.score_mode) return false;
@@ -44,6 +60,20 @@ bool two_pass_plan(const xkv_decode_params* layers, int n, TwoPassPlan* pl) {
   const xkv_decode_params& p = layers[0];
   const int heads = n * p.num_heads;
   pl->heads = heads;
+  pl->dense_values = (n == 1 && dense_values_supported(p)) ? 1 : 0;
+  if (pl->dense_values) {
+    if (!latent_tc_plan(key_logits_call(p), &pl->klat) || !dense_tc_plan(p, &pl->vdense)) return false;
+    size_t off = 0;
+    pl->off_pass1 = off;
+    off += align_up(pl->klat.total_bytes, 256);
+    pl->off_logits = off;
+    off += align_up((size_t)p.batch * heads * p.kv_len * sizeof(float), 256);
+    pl->off_pass2 = off;
+    off += pl->vdense.total_bytes;
+    pl->total_bytes = off;
+    pl->use_pv_tc = 0;
+    return true;
+  }
   // the first pass's workspace leads, so that its status words are the ones the caller reads;
   // the second pass reports into the same words
   size_t off = 0;
@@ -81,6 +111,12 @@ int two_pass_decode(const xkv_decode_params* layers, int n, const TwoPassPlan& p
   const int H = p.num_heads, heads = pl.heads;
   LogitsSink sink{logits, (int64_t)heads * p.kv_len, (int64_t)p.kv_len, (int64_t)H * p.kv_len};
   int rc;
+  if (pl.dense_values) {
+    rc = latent_tc_decode(key_logits_call(p), pl.klat, w + pl.off_pass1, st, &sink);
+    if (rc != XKV_OK) return rc;
+    // the first pass cleared the status words at the head of the workspace; the second reports into them
+    return dense_tc_values_from_logits(p, pl.vdense, sink, w + pl.off_pass2, reinterpret_cast<int*>(w), st);
+  }
   if (p.score_mode == XKV_SCORE_RECON_ROPE) {
     rc = recon_tc_group_decode(layers, n, pl.recon, w + pl.off_pass1, st, &sink);
     if (rc != XKV_OK) return rc;

@@ -81,6 +81,10 @@ struct LogitsSink;
 bool dense_tc_logits_supported(const xkv_decode_params& p);
 int dense_tc_decode(const xkv_decode_params& p, const DenseTcPlan& plan, void* ws, cudaStream_t st,
                     const LogitsSink* sink = nullptr);
+// second pass for keys that are not dense: softmax over fp32 logits, P.V with dense values
+bool dense_tc_values_supported(const xkv_decode_params& p);
+int dense_tc_values_from_logits(const xkv_decode_params& p, const DenseTcPlan& plan, const LogitsSink& logits, void* ws,
+                                int* status, cudaStream_t st);
 
 // ---- shared-latent decode (absorbed factorized K / V, MLA) on mma.sync + TMA (latent_tc_sm100.cu)
 struct LatentTcPlan {
@@ -90,12 +94,21 @@ struct LatentTcPlan {
 };
 bool latent_tc_supported(const xkv_decode_params& p);
 bool latent_tc_plan(const xkv_decode_params& p, LatentTcPlan* plan);
-int latent_tc_decode(const xkv_decode_params& p, const LatentTcPlan& plan, void* ws, cudaStream_t st);
+int latent_tc_decode(const xkv_decode_params& p, const LatentTcPlan& plan, void* ws, cudaStream_t st,
+                     const LogitsSink* sink = nullptr);
 // second pass of a two-pass decode: softmax over fp32 logits of `heads` stacked heads, times the value latent
 bool latent_pv_supported(const xkv_decode_params& p);
 bool latent_pv_plan(const xkv_decode_params& p, int heads, LatentTcPlan* plan);
 int latent_pv_run(const xkv_decode_params& p, int heads, const LatentTcPlan& plan, const float* logits, void* ws,
                   int* status, cudaStream_t st);
+
+// prologue shared by the shared-latent kernels: q_eff[b, h, :] = q . k_proj^T (or q) | q_tail, in the working dtype
+int launch_absorb_query_lowp(const xkv_decode_params& p, void* qeff, int dk, cudaStream_t st);
+
+// ---- shared-latent decode on tcgen05, two CTAs per tile (latent_pair_sm100.cu) -------------------
+bool latent_pair_supported(const xkv_decode_params& p);
+bool latent_pair_plan(const xkv_decode_params& p, LatentTcPlan* plan);
+int latent_pair_decode(const xkv_decode_params& p, const LatentTcPlan& plan, void* ws, cudaStream_t st);
 
 // ---- tcgen05 softmax + P.A_v pass with the output in TMEM (pv_tc_sm100.cu) ------------------------
 struct PvTcPlan {
@@ -109,6 +122,9 @@ int pv_tc_run(const xkv_decode_params& p, int heads, const PvTcPlan& plan, const
 
 // ---- two-pass decode for factorized values behind dense / RoPE-reconstructed keys (two_pass.cu)
 struct TwoPassPlan {
+  int dense_values;          // 1: absorbed factorized keys (no RoPE) in front of dense values
+  LatentTcPlan klat;         //    first pass: shared-latent kernel, logits only
+  DenseTcPlan vdense;        //    second pass: dense kernel, scores from logits
   int heads;                 // layers x heads, stacked for the second pass
   ReconTcPlan recon;
   DenseTcPlan dense;

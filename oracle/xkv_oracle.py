@@ -81,6 +81,22 @@ def gqa_dense(query, key, value, compute_dtype=torch.float32, scale=None):
     return o.reshape(b, H, 1, D)
 
 
+def gqa_dense_multi(query, key, value, attn_mask=None, compute_dtype=torch.float32):
+    """Dense GQA with q_len >= 1 query tokens per sequence and an optional additive mask
+    broadcastable to (b, KVH, G, q_len, L).  attention.py:93-182 (group_query_attentionv2)."""
+    b, H, q_len, D = query.shape
+    _, KVH, L, _ = key.shape
+    G = H // KVH
+    q = _up(query, compute_dtype).reshape(b, KVH, G, q_len, D)
+    k = _up(key, compute_dtype).unsqueeze(2)
+    v = _up(value, compute_dtype).unsqueeze(2)
+    s = torch.matmul(q, k.transpose(-1, -2)) / (D ** 0.5)
+    if attn_mask is not None:
+        s = s + attn_mask.to(s.dtype)
+    p = F.softmax(s, dim=-1, dtype=torch.float32).to(compute_dtype)
+    return torch.matmul(p, v).reshape(b, H, q_len, D)
+
+
 def gqa_factorized_v_only(query, key, value_A, value_B, compute_dtype=torch.float32):
     """Dense K, V = value_A @ value_B.  attention.py:202-274."""
     b, H, q_len, D = query.shape
@@ -251,7 +267,7 @@ def mla_absorbed(q_nope, q_rope, c_kv, k_rope, W_uk, W_uv, sm_scale, compute_dty
     return torch.einsum("bhr,hrv->bhv", o_lat, _up(W_uv, compute_dtype))
 
 
-# --------------------------------------------------------------------------- BASELINE configs
+# --------------------------------------------------------------------------- benchmark configurations
 def rope_query(q, theta, position):
     """Rotate a decode-step query (b,H,1,D) to ``position``.  rope_ref.py:17-21."""
     D = q.shape[-1]

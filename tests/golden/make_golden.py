@@ -14,7 +14,9 @@ import sys
 import numpy as np
 import torch
 
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) != 2:
+    sys.exit("usage: make_golden.py /path/to/reference")
+ref_root = sys.argv[1]
 sys.path.insert(0, ref_root)
 os.environ.setdefault("PYTHONDONTWRITEBYTECODE", "1")
 sys.dont_write_bytecode = True
@@ -104,6 +106,18 @@ for name, b, H, lora, rope, L in [("m1", 2, 4, 16, 8, 29), ("m2", 1, 16, 32, 16,
         # the eager reference DIVIDES by sm_scale; 1/0.25 therefore means "multiply by 0.25"
         o2 = mla_decode_attention_fwd_ref(qn, qr, c, kr, sm_scale=4.0)
     put(f"mla/{name}", q_nope=qn, q_rope=qr, kv_nope=c, k_rope=kr, out_scale1=o1, out_mul_quarter=o2)
+
+# group_query_attentionv2 with several query tokens per sequence (attention.py:93-182), with and
+# without an additive mask; its own seed, so the arrays above do not move when cases are added here
+torch.manual_seed(4321)
+for name, b, H, KVH, D, L, QL in [("v1", 2, 8, 2, 16, 37, 3), ("v2", 1, 4, 4, 32, 20, 5)]:
+    q = torch.randn(b, H, QL, D)
+    K = torch.randn(b, KVH, L, D)
+    V = torch.randn(b, KVH, L, D)
+    mask = torch.randn(b, 1, 1, QL, L)
+    put(f"gqa_v2/{name}", q=q, K=K, V=V, mask=mask,
+        plain=ref_attention.group_query_attentionv2(q, K, V),
+        masked=ref_attention.group_query_attentionv2(q, K, V, attn_mask=mask))
 
 dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_eager.npz")
 np.savez_compressed(dst, **out)

@@ -129,4 +129,8 @@ def test_kernel_selection_is_host_side_and_follows_the_shape():
     packed = dict(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, num_kv_heads=1, head_dim=576, value_dim=512,
                   k_sb=4096 * 576, k_sl=576, k_sh=576, v_sb=4096 * 576, v_sl=576, v_sh=576, q_sb=32 * 576, q_sh=576)
     assert plan(_blk(**packed)) == b"latent_tc"
+    # 64 or more heads: the tcgen05 CTA-pair kernel (heads on the M dimension); a flag keeps the mma.sync one
+    many = dict(packed, num_heads=128, q_sb=128 * 576)
+    assert plan(_blk(**many)) == b"latent_pair"
+    assert plan(_blk(**many, flags=_C.FLAG_LATENT_MMA_SYNC)) == b"latent_tc"
     assert plan(_blk(**packed, logit_cap=5.0)) == b"generic"

@@ -83,7 +83,7 @@ def test_mla(dtype, case):
     kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT, q=qq.to(DEV), k=cd[:, :, 0], v=cd[:, :, 0],
               k_proj=Wk.to(DEV).permute(0, 2, 1).unsqueeze(0), v_proj=Wv.to(DEV).unsqueeze(0), q_tail=qrd,
               k_tail=krd[:, :, 0], sm_scale=sc, num_kv_heads=1)
-    assert ops.plan(**kw) == "latent_tc"
+    assert ops.plan(**kw) == ("latent_pair" if H >= 64 else "latent_tc")
     got2 = K.mla_absorbed_decode(qq.to(DEV), qrd, cd[:, :, 0], krd[:, :, 0], Wk.to(DEV), Wv.to(DEV), sc)
     status_ok()
     close(got2, O.mla_absorbed(qq, qr, c[:, :, 0], kr[:, :, 0], Wk, Wv, sc), "mla_absorbed_decode (latent_tc)")
@@ -101,7 +101,7 @@ def test_packed_single_kv_head_cache(dtype, case):
     kbuf = (torch.randn(b, L, 1, Dk, generator=g) / 3).to(dtype)
     qd, kd = q.to(DEV), kbuf.to(DEV)
     kw = dict(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, q=qd, k=kd, v=kd[..., :Dv], sm_scale=0.4)
-    assert ops.plan(**kw) == "latent_tc"
+    assert ops.plan(**kw) == ("latent_pair" if H >= 64 else "latent_tc")
     o = torch.zeros(b, H, Dv, dtype=dtype, device=DEV)
     assert FD.mla.decode_attention_fwd(qd, kd, kd[..., :Dv], o, 0.4) is None
     status_ok()
@@ -135,3 +135,61 @@ def test_qab_no_pe_logits(dtype, case):
         got = fn(qd, Akd, Bkd)
         status_ok()
         close(got, want, fn.__name__ if hasattr(fn, "__name__") else "qAB_no_pe")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", [(2, 128, 512, 64, 5000, 512), (1, 64, 256, 64, 47, 256), (3, 100, 512, 64, 1000, 512),
+                                  (1, 200, 384, 0, 777, 384), (2, 128, 256, 0, 300, 128)])
+def test_cta_pair_kernel_against_oracle_and_mma_sync_kernel(dtype, case):
+    """The tcgen05 CTA-pair kernel for shared latents (heads on M, the pair splitting the score
+    contraction and the value columns, partial scores exchanged through distributed shared memory)
+    against the oracle and against the mma.sync kernel on the same inputs: 128 heads, fewer than a
+    block, more than a block, with and without the decoupled RoPE part, value columns that are a
+    prefix of the key latent, ragged lengths, and logits that climb so the lazy rescale runs."""
+    b, H, lora, rope, L, Rv = case
+    g = torch.Generator().manual_seed(44)
+    qn = (torch.randn(b, H, lora, generator=g) / 3).to(dtype)
+    c = (torch.randn(b, L, lora, generator=g) / 3).to(dtype)
+    qr = (torch.randn(b, H, rope, generator=g) / 3).to(dtype) if rope else None
+    kr = (torch.randn(b, L, rope, generator=g) / 3).to(dtype) if rope else None
+    dev = lambda x: None if x is None else x.to(DEV)
+    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT, q=dev(qn), k=dev(c), v=dev(c)[..., :Rv], q_tail=dev(qr),
+              k_tail=dev(kr), sm_scale=0.3, num_kv_heads=1)
+    assert ops.plan(**kw) == "latent_pair"
+    got = ops.decode(entry="xkv_mla_decode", **kw)
+    status_ok()
+
+    def ref(qn_, qr_, c_, kr_):
+        s = torch.matmul(qn_.float(), c_.float().transpose(-1, -2))
+        if qr_ is not None:
+            s = s + torch.matmul(qr_.float(), kr_.float().transpose(-1, -2))
+        return torch.matmul(torch.softmax(s * 0.3, -1), c_.float()[..., :Rv])
+
+    close(got, ref(qn, qr, c, kr), "latent_pair vs eager math")
+    alt = ops.decode(entry="xkv_mla_decode", extra_flags=_C.FLAG_LATENT_MMA_SYNC, **kw)
+    close(got, alt.float().cpu(), "latent_pair vs mma.sync kernel", 4e-3, 3e-3)
+    assert torch.equal(got, ops.decode(entry="xkv_mla_decode", **kw))
+    # ragged lengths, NaN past each row's length
+    lens = [L, 1, max(1, L // 2 + 5)][:b]
+    cp = c.clone()
+    krp = None if kr is None else kr.clone()
+    for i, n in enumerate(lens):
+        cp[i, n:] = float("nan")
+        if krp is not None:
+            krp[i, n:] = float("nan")
+    kwr = dict(kw, k=dev(cp), v=dev(cp)[..., :Rv], k_tail=dev(krp), kv_lens=torch.tensor(lens, dtype=torch.int32, device=DEV))
+    got_r = ops.decode(entry="xkv_mla_decode", **kwr)
+    status_ok()
+    for i, n in enumerate(lens):
+        want = ref(qn[i:i + 1], None if qr is None else qr[i:i + 1], c[i:i + 1, :n], None if kr is None else kr[i:i + 1, :n])
+        close(got_r[i:i + 1], want, f"latent_pair ragged row {i}")
+    # climbing logits: keys grow along the context in the direction all queries share
+    u = torch.nn.functional.normalize(torch.randn(lora, generator=g), dim=0)
+    q2 = (3.0 * u + 0.05 * torch.randn(b, H, lora, generator=g)).to(dtype)
+    c2 = ((torch.arange(L, dtype=torch.float32) / 48.0 * 9.0)[None, :, None] * u + 0.05 * torch.randn(b, L, lora, generator=g)).to(dtype)
+    kw2 = dict(kw, q=dev(q2), k=dev(c2), v=dev(c2)[..., :Rv], sm_scale=0.4)
+    got2 = ops.decode(entry="xkv_mla_decode", **kw2)
+    status_ok()
+    close(got2, torch.matmul(torch.softmax((torch.matmul(q2.float(), c2.float().transpose(-1, -2))
+                                            + (0 if qr is None else torch.matmul(qr.float(), kr.float().transpose(-1, -2)))) * 0.4, -1),
+                             c2.float()[..., :Rv]), "latent_pair with climbing logits")

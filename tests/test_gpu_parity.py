@@ -19,6 +19,7 @@ from oracle import xkv_oracle as O
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_eager.npz"))
 
 
 def tol(dtype):
@@ -478,3 +479,40 @@ def test_latent_append_roundtrip(dtype):
     for i, n in enumerate(lens):
         want = O.gqa_factorized(q[i:i + 1], Ac[i:i + 1, :n + 1], Bk[i:i + 1], V[i:i + 1, :n + 1], Bk[i:i + 1])
         check(got[i:i + 1], want, dtype, f"decode after append, row {i}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_several_query_tokens_v2(dtype):
+    """group_query_attentionv2 with q_len > 1 (attention.py:93-182): the reference's own outputs on the
+    golden inputs, then a speculative-decode shape (4 new tokens, causal among themselves through the
+    additive mask) on head_dim 128 where group x q_len = 16 rows stay on the tensor-core kernel, and a
+    longer burst that goes to the portable kernel."""
+    if dtype == torch.float32:
+        for name in ("v1", "v2"):
+            p = f"gqa_v2/{name}/"
+            q, Kc, V, mask = (torch.from_numpy(GOLD[p + k]) for k in ["q", "K", "V", "mask"])
+            got = K.group_query_attentionv2(q.to(DEV), Kc.to(DEV), V.to(DEV))
+            check(got, torch.from_numpy(GOLD[p + "plain"]), dtype, f"golden v2 {name}")
+            got = K.group_query_attentionv2(q.to(DEV), Kc.to(DEV), V.to(DEV), attn_mask=mask.to(DEV))
+            check(got, torch.from_numpy(GOLD[p + "masked"]), dtype, f"golden v2 {name} masked")
+    b, H, KVH, D, L = 2, 32, 8, 128, 700
+    gen = g(16)
+    k, kd = mk((b, KVH, L, D), dtype, gen=gen)
+    v, vd = mk((b, KVH, L, D), dtype, gen=gen)
+    for q_len in (4, 7):
+        q, qd = mk((b, H, q_len, D), dtype, gen=gen)
+        got = K.group_query_attentionv2(qd, kd, vd)
+        check(got, O.gqa_dense_multi(q, k, v), dtype, f"q_len {q_len}")
+        # the last q_len cache rows are the new tokens: token t may not see the ones after it
+        causal = torch.zeros(q_len, L)
+        for t_ in range(q_len):
+            causal[t_, L - q_len + t_ + 1:] = float("-inf")
+        got = K.group_query_attentionv2(qd, kd, vd, attn_mask=causal.to(dtype).to(DEV))
+        check(got, O.gqa_dense_multi(q, k, v, causal), dtype, f"q_len {q_len} causal")
+        # each query token alone is the single-step call
+        one = K.group_query_attention(qd[:, :, 1:2].contiguous(), kd, vd)
+        check(K.group_query_attentionv2(qd, kd, vd)[:, :, 1:2], one.float().cpu(), dtype, "one token of the burst")
+    if dtype != torch.float32:
+        q4 = torch.zeros(b, H * 4, D, dtype=dtype, device=DEV)
+        assert ops.plan(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, q=q4, k=kd.transpose(1, 2), v=vd.transpose(1, 2),
+                        sm_scale=1.0) == "dense_tc"

@@ -153,3 +153,41 @@ def test_second_pass_kernels_agree():
     got = K.recon_rope_decode(q, A, B, Av, Bv, theta=theta)
     alt = K.recon_rope_decode(q, A, B, Av, Bv, theta=theta, pv_mma_sync=True)
     close(got, alt.float().cpu(), "tcgen05 vs mma.sync second pass", 4e-3, 3e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", [(1, 32, 8, 4096, 256), (3, 64, 8, 1000, 128), (2, 8, 8, 130, 512), (2, 32, 2, 777, 192)])
+def test_factorized_keys_with_dense_values(dtype, case):
+    """Factorized K without RoPE in front of dense V (the reference's k_only fused kernel,
+    flash_recontruction/fused_attention/no_pe/v1_k_only.py:368-465; configuration 1's dataflow): logits on
+    the shared-latent tensor-core kernel in absorbed order, softmax and P.V on the dense-value kernel."""
+    from kernel_collections_b200 import flash_recontruction as FR
+    b, H, kvh, L, R = case
+    g = torch.Generator().manual_seed(57)
+    q = torch.randn(b, H, D, generator=g).to(dtype)
+    A = torch.randn(b, L, R, generator=g).to(dtype)
+    Bk = (torch.randn(b, kvh, R, D, generator=g) / R ** 0.5).to(dtype)
+    V = torch.randn(b, L, kvh, D, generator=g).to(dtype)
+    qd, Ad, Bd, Vd = (x.to(DEV) for x in (q, A, Bk, V))
+    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_DENSE, q=qd, k=Ad, k_proj=Bd, v=Vd, sm_scale=D ** -0.5)
+    assert ops.plan(**kw) == "two_pass"
+    o = torch.empty(b, H, D, dtype=dtype, device=DEV)
+    got = FR.gqa_xKV_no_pe_k_only(qd, Ad, Bd, Vd, o, torch.full((b,), 4, dtype=torch.int32, device=DEV), 4, sm_scale=D ** -0.5)
+    rc, detail = _C.last_status(torch.device(DEV))
+    assert rc == 0, detail
+    assert got is o
+    close(got, O.xkv_fused_k_only(q, A, Bk, V, sm_scale=D ** -0.5), "k_only two-pass vs oracle")
+    gen = ops.decode(entry="xkv_absorbed_decode", force_generic=True, **kw)
+    close(got, gen.float().cpu(), "k_only two-pass vs portable kernel", 1e-2, 6e-3)
+    assert torch.equal(got, ops.decode(entry="xkv_absorbed_decode", **kw))
+    # ragged rows, NaN past each row's length
+    lens = [L, 1, L // 2 + 3][:b]
+    Ap, Vp = A.clone(), V.clone()
+    for i, n in enumerate(lens):
+        Ap[i, n:] = float("nan")
+        Vp[i, n:] = float("nan")
+    got_r = ops.decode(entry="xkv_absorbed_decode", **dict(kw, k=Ap.to(DEV), v=Vp.to(DEV),
+                                                           kv_lens=torch.tensor(lens, dtype=torch.int32, device=DEV)))
+    for i, n in enumerate(lens):
+        close(got_r[i:i + 1], O.xkv_fused_k_only(q[i:i + 1], A[i:i + 1, :n], Bk[i:i + 1], V[i:i + 1, :n], sm_scale=D ** -0.5),
+              f"k_only ragged row {i}")

@@ -78,3 +78,13 @@ def test_dense_v_as_identity_factorization():
     ref = O.gqa_factorized(q, A, B, vA, vB)
     got = O.xkv_fused_k_only(q.squeeze(2), A, B, V, D ** -0.5)
     close(got, ref.squeeze(2), 1e-5)
+
+
+@pytest.mark.parametrize("name", ["v1", "v2"])
+def test_gqa_v2_several_query_tokens(name):
+    p = f"gqa_v2/{name}/"
+    q, K, V, mask = (t(p + k) for k in ["q", "K", "V", "mask"])
+    close(O.gqa_dense_multi(q, K, V), t(p + "plain"))
+    close(O.gqa_dense_multi(q, K, V, mask), t(p + "masked"))
+    # one query token at a time is the single-step function
+    close(O.gqa_dense_multi(q, K, V)[:, :, 1:2], O.gqa_dense(q[:, :, 1:2], K, V))
