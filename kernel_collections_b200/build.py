@@ -102,5 +102,17 @@ def build(force: bool = False, verbose: bool = False, defines=(), lib_path: str 
     return lib_path
 
 
+FAULT_TEST_LIB = os.path.join(PKG_DIR, "libxkv_faulttest.so")
+
+
+def build_fault_test(force: bool = False) -> str:
+    """The test-only copy of the library (-DXKV_FAULT_TEST): device-side waits give up after 20 ms and a
+    flag bit makes one kernel's producer skip a load it announced.  tests/test_gpu_timeout.py uses it to
+    run the time-out path on purpose; the regular library is not affected."""
+    if not force and not _stale(FAULT_TEST_LIB, sources() + _headers()):
+        return FAULT_TEST_LIB
+    return build(defines=["XKV_FAULT_TEST"], lib_path=FAULT_TEST_LIB)
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

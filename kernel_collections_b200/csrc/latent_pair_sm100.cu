@@ -3,17 +3,21 @@
 //
 // Up to 128 query heads sit on the M dimension of every MMA.  The output rows O[128 x Rv] (fp32)
 // alone would fill the 512 tensor-memory columns of an SM, and the resident queries Q[128 x Dk] most
-// of its shared memory, so a CLUSTER OF TWO CTAs shares each 48-token tile:
+// of its shared memory, so a CLUSTER OF TWO CTAs shares each 32-token tile:
 //   * CTA r owns half of the value columns (O[128 x Rv/2] stays in its tensor memory for the whole
 //     split) and half of the score contraction: it keeps the matching 64-wide blocks of Q resident,
 //     streams only those blocks of the latent rows (each latent byte is fetched by exactly one of the
 //     two CTAs, so the pair reads the cache once), and forms S_r = Q_r . K_r^T on the tensor core;
-//   * the two partial score tiles are exchanged through distributed shared memory (plain 128-bit
-//     stores into the peer's buffer + an mbarrier arrive, no multicast) and added; both CTAs then
+//   * the two partial score tiles are exchanged through distributed shared memory (each warp stages its
+//     share and sends it with one cp.async.bulk into the peer's buffer, which counts the bytes on the peer's
+//     mbarrier; no multicast, no fences on the sender) and added; both CTAs then
 //     hold the same S, run the same softmax (one thread per head row, lazily updated reference
 //     maximum as in the two-pass value kernel) and multiply their own value columns: O_r += P . V_r.
-// Warps: 0 TMA producer (3-stage ring of whole tiles), 1 MMA issuer (S of tile i+1 is issued before
-// P.V of tile i: two score buffers in tensor memory), 2 tensor-memory allocation, 4-7 softmax.
+// Warps: 0 TMA producer (4-stage ring of whole tiles), 1 MMA issuer (the scores run two tiles ahead of
+// P.V: three score buffers in tensor memory), 2 tensor-memory allocation, 4-11 softmax (two threads per
+// head row, 16 tokens of the tile each; a tile's partial scores are sent to the peer one tile early, so
+// the exchange hides under the previous tile's exponentials: the softmax chain, not the tensor core or
+// HBM, paces this kernel).
 // Every wait is bounded; on expiry the CTA raises its abort flag, reports where it gave up, drains,
 // frees its tensor memory and leaves (the peer's waits then run out the same way).
 #include "sm100_common.cuh"
@@ -22,25 +26,29 @@ namespace xkv {
 using namespace sm100;
 namespace {
 
-constexpr int T = 48;                        // tokens per tile
+constexpr int T = 32;                        // tokens per tile
 constexpr int MAXB = 5;                      // 64-column blocks per CTA and tile
-constexpr int BLK = T * 128;                 // bytes of one [48 tokens x 64 columns] block
-constexpr int STAGES = 3;
+constexpr int BLK = T * 128;                 // bytes of one [32 tokens x 64 columns] block
+constexpr int STAGES = 4;
 constexpr int QBLK = 128 * 128;              // bytes of one [128 heads x 64 columns] query block
-constexpr int NTHREADS = 256;
+constexpr int NTHREADS = 384;
+constexpr int TH = T / 2;                     // tokens per softmax thread (two threads share a head row)
 constexpr int OFF_Q = 0;
 constexpr int OFF_RING = OFF_Q + MAXB * QBLK;                 // 81920
-constexpr int OFF_P = OFF_RING + STAGES * MAXB * BLK;         // 174080
-constexpr int P_BYTES = 128 * 128;                            // 128 head rows x 64 token slots (48 used)
-constexpr int OFF_X = OFF_P + P_BYTES;                        // 190464: partial scores from the peer
-constexpr int X_BYTES = (T / 4) * 128 * 16;                   // [T/4][128 rows][4 floats] = 24576
-constexpr int OFF_BAR = OFF_X + X_BYTES;                      // 215040
-constexpr int OFF_MISC = OFF_BAR + 16 * 8;
-constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;
+constexpr int OFF_P = OFF_RING + STAGES * MAXB * BLK;
+constexpr int P_BYTES = 128 * 128;                            // 128 head rows x 64 token slots (32 used)
+constexpr int OFF_X = OFF_P + P_BYTES;                        // partial scores from the peer
+constexpr int X_BYTES = (T / 4) * 128 * 16;                   // [T/4][128 rows][4 floats] = 16384
+constexpr int XW_BYTES = X_BYTES / 8;                         // one softmax warp's share of an exchange buffer
+constexpr int OFF_BAR = OFF_X + 2 * X_BYTES;                  // two exchange buffers, alternating per tile
+constexpr int OFF_MISC = OFF_BAR + 20 * 8;
+constexpr int OFF_RED = OFF_MISC + 16;                        // [2][128] floats: per-half row maxima / sums
+constexpr int SMEM_BYTES = OFF_RED + 1024 + 1024;
 static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
 static_assert(OFF_RING % 1024 == 0 && BLK % 1024 == 0 && OFF_P % 1024 == 0, "swizzled blocks need 1024-byte alignment");
 constexpr float RESCALE_THRESHOLD = 8.f;
-constexpr uint32_t S_COL0 = 256;             // tensor-memory columns: O in 0..255, two score buffers at 256 / 320
+constexpr uint32_t S_COL0 = 256;             // tensor-memory columns: O in 0..255, three score buffers of 32 from 256
+constexpr int SBUF = 3;
 
 // The 64-column blocks one CTA of the pair works on.  Blocks [0, nv) are its own value columns (in
 // alias mode they are score blocks too); blocks with score[i] set take part in S.
@@ -78,12 +86,16 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void st_remote_v4(uint32_t cluster_addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c), "f"(d)
+// One bulk copy from this CTA's shared memory into the peer's, counting its bytes on an mbarrier of the peer.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, uint32_t src_local, uint32_t bytes, uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster), "r"(src_local), "r"(bytes), "r"(bar_cluster)
                : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 // Bounded wait whose acquire covers writes made by the other CTA of the cluster.
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -108,6 +120,28 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
   return false;
 }
 
+#ifdef XKV_TC_PROFILE
+// Debug build only: cycles spent in each kind of wait, summed over CTAs into status[8 + 2 * slot] (64-bit).
+#define XKV_LP_WAIT(slot, leader, expr)                                              \
+  [&]() {                                                                            \
+    const long long t0_ = clock64();                                                 \
+    const bool r_ = (expr);                                                          \
+    if (leader)                                                                      \
+      atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + (slot),        \
+                (unsigned long long)(clock64() - t0_));                              \
+    return r_;                                                                       \
+  }()
+#define XKV_LP_MARK(slot)                                                                         \
+  do {                                                                                            \
+    const long long now_ = clock64();                                                             \
+    if (threadIdx.x == 128) atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + (slot), (unsigned long long)(now_ - mark_)); \
+    mark_ = now_;                                                                                 \
+  } while (0)
+#else
+#define XKV_LP_WAIT(slot, leader, expr) (expr)
+#define XKV_LP_MARK(slot) do { } while (0)
+#endif
+
 template <typename T_>
 __global__ void __launch_bounds__(NTHREADS, 1)
 latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmKt,
@@ -131,24 +165,22 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const uint32_t stage_bytes = (uint32_t)bl.n * BLK;
 
   const uint32_t bar0 = base + OFF_BAR;
-  auto bar_full = [&](int s) { return bar0 + 8u * s; };
-  auto bar_empty = [&](int s) { return bar0 + 8u * (3 + s); };
-  auto bar_sfull = [&](int i) { return bar0 + 8u * (6 + i); };
-  auto bar_sempty = [&](int i) { return bar0 + 8u * (8 + i); };
-  const uint32_t bar_pfull = bar0 + 8u * 10, bar_pempty = bar0 + 8u * 11, bar_odone = bar0 + 8u * 12;
-  const uint32_t bar_xfull = bar0 + 8u * 13;    // the peer's partial scores have landed in my buffer
-  const uint32_t bar_xfree = bar0 + 8u * 14;    // the peer has read its buffer: I may write the next tile into it
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };               // [4] a tile's blocks have landed
+  auto bar_empty = [&](int s) { return bar0 + 8u * (4 + s); };        // [4] P.V of the tile that used the stage has run
+  auto bar_sfull = [&](int i) { return bar0 + 8u * (8 + i); };        // [3] a score buffer holds S of a tile
+  auto bar_sempty = [&](int i) { return bar0 + 8u * (11 + i); };      // [3] the softmax threads have read it
+  const uint32_t bar_pfull = bar0 + 8u * 14, bar_pempty = bar0 + 8u * 15, bar_odone = bar0 + 8u * 16;
+  auto bar_xfull = [&](int i) { return bar0 + 8u * (17 + i); };       // [2] the peer's partial scores have landed in exchange buffer i
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 4);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_sfull(i), 1); mbar_init(bar_sempty(i), 128); }
-    mbar_init(bar_pfull, 128);
+    for (int i = 0; i < SBUF; ++i) { mbar_init(bar_sfull(i), 1); mbar_init(bar_sempty(i), 256); }
+    mbar_init(bar_pfull, 256);
     mbar_init(bar_pempty, 1);
     mbar_init(bar_odone, 1);
-    mbar_init(bar_xfull, 128);
-    mbar_init(bar_xfree, 128);
+    for (int i = 0; i < 2; ++i) mbar_init(bar_xfull(i), 1);   // one local arrive.expect_tx per use + the peer's st.async bytes
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -178,13 +210,17 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   cluster_sync_all();          // the peer's barriers exist before anything is signalled across CTAs
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+#ifdef XKV_TC_PROFILE
+  const long long t_start_ = clock64();
+  const uint64_t ns_start_ = global_ns();
+#endif
 
   if (warp == 0) {
     // =========================== producer: whole tiles of this CTA's blocks ========================
     if (lane == 0) {
       for (int i = 0; i < ntiles; ++i) {
         const int stage = i % STAGES;
-        if (!mbar_wait(bar_empty(stage), ((uint32_t)(i / STAGES) & 1u) ^ 1u, abort_flag)) {
+        if (!XKV_LP_WAIT(0, true, mbar_wait(bar_empty(stage), ((uint32_t)(i / STAGES) & 1u) ^ 1u, abort_flag))) {
           report(a.status, XKV_ERR_TIMEOUT, 30, tile_begin + i, (int)rank, b);
           break;
         }
@@ -206,12 +242,12 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       const uint32_t idesc_o = (1u << 4) | (kfmt << 7) | (kfmt << 10) | (1u << 16) | (((uint32_t)nvc >> 3) << 17) |
                                ((128u >> 4) << 24);
       auto issue_scores = [&](int i) -> bool {
-        const int stage = i % STAGES, sb = i & 1;
-        if (i >= 2 && !mbar_wait(bar_sempty(sb), ((uint32_t)((i - 2) >> 1) & 1u), abort_flag)) return false;
-        if (!mbar_wait(bar_full(stage), (uint32_t)(i / STAGES) & 1u, abort_flag)) return false;
+        const int stage = i % STAGES, sb = i % SBUF;
+        if (i >= SBUF && !XKV_LP_WAIT(1, true, mbar_wait(bar_sempty(sb), ((uint32_t)(i / SBUF) & 1u) ^ 1u, abort_flag))) return false;
+        if (!XKV_LP_WAIT(2, true, mbar_wait(bar_full(stage), (uint32_t)(i / STAGES) & 1u, abort_flag))) return false;
         tc_fence_after();
         const uint32_t ss = base + OFF_RING + stage * (MAXB * BLK);
-        const uint32_t tacc = tmem_base + S_COL0 + (uint32_t)sb * 64u;
+        const uint32_t tacc = tmem_base + S_COL0 + (uint32_t)sb * (uint32_t)T;
         int qi = 0;
         bool first = true;
         for (int k = 0; k < bl.n; ++k) {
@@ -228,11 +264,14 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         tc_commit(bar_sfull(sb));
         return true;
       };
+      // the scores run two tiles ahead of P.V: S(i+2) is in the queue before P of tile i is waited for, so the
+      // softmax threads find S(i+1) finished when they turn to it in the middle of tile i
       bool ok = issue_scores(0);
+      if (ok && ntiles > 1) ok = issue_scores(1);
       for (int i = 0; ok && i < ntiles; ++i) {
-        if (i + 1 < ntiles) ok = issue_scores(i + 1);
+        if (i + 2 < ntiles) ok = issue_scores(i + 2);
         if (!ok) break;
-        if (!mbar_wait(bar_pfull, (uint32_t)i & 1u, abort_flag)) { ok = false; break; }
+        if (!XKV_LP_WAIT(3, true, mbar_wait(bar_pfull, (uint32_t)i & 1u, abort_flag))) { ok = false; break; }
         tc_fence_after();
         const uint32_t ss = base + OFF_RING + (i % STAGES) * (MAXB * BLK);
 #pragma unroll
@@ -248,86 +287,119 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       else report(a.status, XKV_ERR_TIMEOUT, 31, tile_begin, (int)rank, b);
     }
   } else if (warp >= 4) {
-    // =========================== softmax: one thread per head row =====================================
-    const int r = threadIdx.x - 128;
+    // =========================== softmax: two threads per head row, 16 tokens of the tile each =========
+    const int r = (threadIdx.x - 128) & 127;                 // head row = tensor-memory lane
+    const int half = (threadIdx.x - 128) >> 7;               // warps 4-7: tokens 0-15, warps 8-11: tokens 16-31
     const int h = h0 + r;
     const bool live = h < a.num_heads;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t x_local = base + OFF_X + (uint32_t)r * 16u;            // [g][row][4]: + g * 2048
-    const uint32_t x_peer = map_to_cta(x_local, peer);
-    const uint32_t xfull_peer = map_to_cta(bar_xfull, peer), xfree_peer = map_to_cta(bar_xfree, peer);
-    float m_ref = -CUDART_INF_F, l_sum = 0.f;
+    // exchange buffers: [buffer 2][softmax warp 8][group of 4 tokens][lane][4 floats]: a warp's share is 2 KB in one piece
+    const uint32_t x_warp = base + OFF_X + (uint32_t)(warp - 4) * XW_BYTES;          // + buffer * X_BYTES
+    const uint32_t x_local = x_warp + (uint32_t)lane * 16u;                             // + g * 512
+    const uint32_t x_warp_peer = map_to_cta(x_warp, peer);
+    float* red_s = reinterpret_cast<float*>(sm + OFF_RED);   // [2][128]: per-half row maxima / row sums
+    float m_ref = -CUDART_INF_F, l_sum = 0.f;                // l_sum: this thread's tokens only
     bool alive = true;
-    for (int i = 0; i < ntiles && alive; ++i) {
-      const int sb = i & 1;
-      // ---- own partial scores out of tensor memory ---------------------------------------------------
-      if (!mbar_wait(bar_sfull(sb), (uint32_t)(i >> 1) & 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 32, tile_begin + i, (int)rank, b);
+    // My partial scores of a tile leave tensor memory and go to the peer one tile EARLY (in the middle of
+    // the previous tile's softmax), so the exchange's latency hides under that tile's exponentials.  Two
+    // exchange buffers with a barrier each.  The partial of tile t is staged in MY buffer (t + 1) & 1 (the one I
+    // have just read tile t - 1 out of: the peer cannot write tile t + 1 into it before it has this very
+    // copy) and bulk-copied, one 2 KB piece per warp, into the PEER's buffer t & 1, counting its bytes there.
+    float s[TH], s_next[TH];
+    auto fetch_and_send = [&](int i) {
+      const int sb = i % SBUF;
+      if (!XKV_LP_WAIT(4, threadIdx.x == 128, mbar_wait(bar_sfull(sb), (uint32_t)(i / SBUF) & 1u, abort_flag))) report(a.status, XKV_ERR_TIMEOUT, 32, tile_begin + i, (int)rank, b);
       tc_fence_after();
-      float s[T];
-      {
-        uint32_t v[16];
+      uint32_t v0[16];
+      static_assert(TH == 16, "one 16-column load per thread and tile");
+      tmem_ld16(lane_addr + S_COL0 + (uint32_t)sb * (uint32_t)T + (uint32_t)(half * TH), v0);
+      tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < T; c += 16) {
-          tmem_ld16(lane_addr + S_COL0 + (uint32_t)sb * 64u + c, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) s[c + e] = __uint_as_float(v[e]);
-        }
-      }
+      for (int e = 0; e < 16; ++e) s_next[e] = __uint_as_float(v0[e]);
       tc_fence_before();
       mbar_arrive(bar_sempty(sb));
-      // ---- exchange with the peer: my partial into its buffer, its partial out of mine ------------------
-      if (i > 0 && !mbar_wait_cluster(bar_xfree, (uint32_t)(i - 1) & 1u, abort_flag))
-        report(a.status, XKV_ERR_TIMEOUT, 33, tile_begin + i, (int)rank, b);
+      const uint32_t stage_off = (uint32_t)((i + 1) & 1) * X_BYTES, dst_off = (uint32_t)(i & 1) * X_BYTES;
+      if (threadIdx.x == 128) mbar_expect_tx(bar_xfull(i & 1), X_BYTES);   // my buffer i & 1: all of the peer's bytes for tile i
 #pragma unroll
-      for (int g4 = 0; g4 < T / 4; ++g4)
-        st_remote_v4(x_peer + g4 * 2048, s[4 * g4], s[4 * g4 + 1], s[4 * g4 + 2], s[4 * g4 + 3]);
-      mbar_arrive_remote(xfull_peer);
-      if (!mbar_wait_cluster(bar_xfull, (uint32_t)i & 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 34, tile_begin + i, (int)rank, b);
-      const int t0 = (tile_begin + i) * T;
+      for (int g4 = 0; g4 < TH / 4; ++g4)
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(x_local + stage_off + g4 * 512), "f"(s_next[4 * g4]),
+                     "f"(s_next[4 * g4 + 1]), "f"(s_next[4 * g4 + 2]), "f"(s_next[4 * g4 + 3]) : "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");         // generic writes -> the bulk copy's reads
+      __syncwarp();
+      if (lane == 0)
+        bulk_copy_to_peer(x_warp_peer + dst_off, x_warp + stage_off, XW_BYTES, map_to_cta(bar_xfull(i & 1), peer));
+    };
+    if (ntiles > 0) fetch_and_send(0);
+    for (int i = 0; i < ntiles && alive; ++i) {
+#ifdef XKV_TC_PROFILE
+      long long mark_ = clock64();
+#endif
 #pragma unroll
-      for (int g4 = 0; g4 < T / 4; ++g4) {
+      for (int e = 0; e < TH; ++e) s[e] = s_next[e];
+      // ---- the peer's partial of this tile (sent a tile ago) + mine ------------------------------------
+      const uint32_t xoff = (uint32_t)(i & 1) * X_BYTES;
+      if (!XKV_LP_WAIT(6, threadIdx.x == 128, mbar_wait_cluster(bar_xfull(i & 1), (uint32_t)(i >> 1) & 1u, abort_flag))) report(a.status, XKV_ERR_TIMEOUT, 34, tile_begin + i, (int)rank, b);
+      const int t0 = (tile_begin + i) * T + half * TH;       // first token of this thread
+      XKV_LP_MARK(12);
+#pragma unroll
+      for (int g4 = 0; g4 < TH / 4; ++g4) {
         float4 o;
-        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(o.x), "=f"(o.y), "=f"(o.z), "=f"(o.w) : "r"(x_local + g4 * 2048));
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(o.x), "=f"(o.y), "=f"(o.z), "=f"(o.w) : "r"(x_local + xoff + g4 * 512));
         // (a + b == b + a exactly: both CTAs end up with the same bits)
         s[4 * g4] = (s[4 * g4] + o.x) * a.scale_log2;
         s[4 * g4 + 1] = (s[4 * g4 + 1] + o.y) * a.scale_log2;
         s[4 * g4 + 2] = (s[4 * g4 + 2] + o.z) * a.scale_log2;
         s[4 * g4 + 3] = (s[4 * g4 + 3] + o.w) * a.scale_log2;
       }
-      mbar_arrive_remote(xfree_peer);
+      XKV_LP_MARK(13);
+      // ---- next tile's partial on its way while this tile's softmax runs --------------------------------
+      if (i + 1 < ntiles) fetch_and_send(i + 1);
+      XKV_LP_MARK(11);
+      if (t0 + TH > row_len || !live) {
+#pragma unroll
+        for (int e = 0; e < TH; ++e)
+          if (t0 + e >= row_len || !live) s[e] = -CUDART_INF_F;
+      }
       float tmax = -CUDART_INF_F;
 #pragma unroll
-      for (int e = 0; e < T; ++e) {
-        if (t0 + e >= row_len || !live) s[e] = -CUDART_INF_F;
-        tmax = fmaxf(tmax, s[e]);
-      }
-      // ---- lazily updated reference maximum; all 128 rows agree on whether to rescale -------------------
-      const bool move = tmax > m_ref + RESCALE_THRESHOLD || (m_ref == -CUDART_INF_F && tmax > -CUDART_INF_F);
+      for (int e = 0; e < TH; ++e) tmax = fmaxf(tmax, s[e]);
+      XKV_LP_MARK(10);
+      // ---- lazily updated reference maximum: does ANY thread see a score that tops its row's reference by
+      // more than the threshold (or a first finite score)?  All 256 agree through one reducing barrier.
+      const bool move_hint = tmax > m_ref + RESCALE_THRESHOLD || (m_ref == -CUDART_INF_F && tmax > -CUDART_INF_F);
       uint32_t anym, anya;
       {
-        const uint32_t mine = (move ? 1u : 0u) | (*abort_flag ? 2u : 0u);
+        const uint32_t mine = (move_hint ? 1u : 0u) | (*abort_flag ? 2u : 0u);
         asm volatile(
             "{\n\t.reg .pred p, q;\n\t"
             "setp.ne.u32 p, %2, 0;\n\t"
-            "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
+            "barrier.cta.red.or.pred q, 1, 256, p;\n\t"
             "selp.u32 %0, 1, 0, q;\n\t"
             "setp.ne.u32 p, %3, 0;\n\t"
-            "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
+            "barrier.cta.red.or.pred q, 1, 256, p;\n\t"
             "selp.u32 %1, 1, 0, q;\n\t}"
             : "=r"(anym), "=r"(anya)
             : "r"(mine & 1u), "r"(mine & 2u)
             : "memory");
       }
       if (anya) { alive = false; break; }
+      XKV_LP_MARK(14);
       // the single P buffer (and, for a rescale, the output rows) are free once P.V of the previous tile has run
-      if (i > 0 && !mbar_wait(bar_pempty, (uint32_t)(i - 1) & 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 35, tile_begin + i, (int)rank, b);
+      if (i > 0 && !XKV_LP_WAIT(7, threadIdx.x == 128, mbar_wait(bar_pempty, (uint32_t)(i - 1) & 1u, abort_flag))) report(a.status, XKV_ERR_TIMEOUT, 35, tile_begin + i, (int)rank, b);
       if (anym) {
-        const float m_new = move ? tmax : m_ref;
-        const float alpha = (m_ref == -CUDART_INF_F) ? 0.f : exp2f(m_ref - m_new);
+        // rare: the two threads of a row put their maxima together, every row decides for itself, and each
+        // thread rescales its half of the row's output columns in tensor memory
+        red_s[half * 128 + r] = tmax;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float rmax = fmaxf(red_s[r], red_s[128 + r]);
+        asm volatile("bar.sync 1, 256;" ::: "memory");        // (the slots are reused by the next rescale)
+        const bool move = rmax > m_ref + RESCALE_THRESHOLD || (m_ref == -CUDART_INF_F && rmax > -CUDART_INF_F);
+        const float m_new = move ? rmax : m_ref;
+        const float alpha = (m_ref == -CUDART_INF_F) ? 0.f : ex2_approx(m_ref - m_new);
         if (i > 0) {
           tc_fence_after();
-          for (int c = 0; c < nvc; c += 32) {
+          const int c0 = half * (nvc / 2);
+          for (int c = c0; c < c0 + nvc / 2; c += 32) {
             uint32_t v[32];
             tmem_ld32(lane_addr + c, v);
             tmem_wait_ld();
@@ -341,45 +413,53 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         l_sum *= alpha;
         m_ref = m_new;
       }
+      XKV_LP_MARK(15);
       // ---- P row -> shared memory (K-major, 128-byte swizzle), row sum of the rounded values ------------
       const float mref = m_ref == -CUDART_INF_F ? 0.f : m_ref;
       uint8_t* prow = sm + OFF_P + r * 128;
 #pragma unroll
-      for (int c8 = 0; c8 < T / 8; ++c8) {
+      for (int c8 = 0; c8 < TH / 8; ++c8) {
         uint32_t pk[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = exp2f(s[c8 * 8 + 2 * e] - mref), p1 = exp2f(s[c8 * 8 + 2 * e + 1] - mref);
+          const float p0 = ex2_approx(s[c8 * 8 + 2 * e] - mref), p1 = ex2_approx(s[c8 * 8 + 2 * e + 1] - mref);
           T_ q0 = TypeTraits<T_>::from_f(p0), q1 = TypeTraits<T_>::from_f(p1);
           l_sum += TypeTraits<T_>::to_f(q0) + TypeTraits<T_>::to_f(q1);
           pk[e] = (uint32_t)(*reinterpret_cast<uint16_t*>(&q0)) | ((uint32_t)(*reinterpret_cast<uint16_t*>(&q1)) << 16);
         }
-        *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(prow + (((half * (TH / 8) + c8) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       // ragged batch, last tile of the row: value rows past the row's own length may hold anything (NaN
       // included, and 0 * NaN is NaN): zero them before the MMAs read the tile
-      if (a.kv_lens != nullptr && t0 + T > row_len) {
+      const int tile0 = (tile_begin + i) * T;
+      if (a.kv_lens != nullptr && tile0 + T > row_len) {
         const int stage = i % STAGES;
         if (!mbar_wait(bar_full(stage), (uint32_t)(i / STAGES) & 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 36, tile_begin + i, (int)rank, b);
-        const int first = max(row_len - t0, 0), per_row = bl.nv * 8;
-        for (int idx = r; idx < (T - first) * per_row; idx += 128) {
+        const int first = max(row_len - tile0, 0), per_row = bl.nv * 8;
+        for (int idx = threadIdx.x - 128; idx < (T - first) * per_row; idx += 256) {
           const int row = first + idx / per_row, rem = idx % per_row;
           *reinterpret_cast<uint4*>(sm + OFF_RING + stage * (MAXB * BLK) + (rem >> 3) * BLK + row * 128 + (rem & 7) * 16) =
               make_uint4(0u, 0u, 0u, 0u);
         }
       }
+      XKV_LP_MARK(16);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
       mbar_arrive(bar_pfull);
+      XKV_LP_MARK(17);
     }
-    // ---- output: O row / l, log-sum-exp ---------------------------------------------------------------
+    // ---- output: O row / l, log-sum-exp; each thread writes its half of the row's columns ---------------
     if (alive && ntiles > 0) {
-      if (!mbar_wait(bar_odone, 0, abort_flag)) { report(a.status, XKV_ERR_TIMEOUT, 37, tile_end, (int)rank, b); alive = false; }
+      if (!mbar_wait(bar_odone, 0, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 37, tile_end, (int)rank, b);
       tc_fence_after();
     }
+    red_s[half * 128 + r] = l_sum;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     if (alive && !*abort_flag) {
-      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      const float l_row = red_s[r] + red_s[128 + r];          // fixed order: identical in both threads and both CTAs
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+      const int c0 = half * (nvc / 2);
       float* po = a.partial_o + (((int64_t)b * a.num_heads + (live ? h : 0)) * a.num_splits + split) * a.rv + col_out;
-      for (int c = 0; c < nvc; c += 32) {
+      for (int c = c0; c < c0 + nvc / 2; c += 32) {
         uint32_t v[32];
         if (ntiles > 0) {                    // (warp-wide tensor-memory load: rows past the last head take part)
           tmem_ld32(lane_addr + c, v);
@@ -396,12 +476,18 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                             __uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
         }
       }
-      if (live && rank == 0)
+      if (live && rank == 0 && half == 0)
         a.lse[((int64_t)b * a.num_heads + h) * a.num_splits + split] =
-            l_sum > 0.f ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -CUDART_INF_F;
+            l_row > 0.f ? (m_ref + log2f(l_row)) * 0.6931471805599453f : -CUDART_INF_F;
     }
   }
 
+#ifdef XKV_TC_PROFILE
+  if (threadIdx.x == 128)
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 8, (unsigned long long)(clock64() - t_start_));
+  if (threadIdx.x == 128)
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 9, (unsigned long long)(global_ns() - ns_start_));
+#endif
   __syncwarp();
   tc_fence_before();
   __syncthreads();
@@ -448,10 +534,8 @@ bool make_lists(const xkv_decode_params& p, BlockList out[2]) {
   }
   // score blocks not covered above: all key blocks (separate value latent) or the key blocks past the
   // value columns (alias), then the decoupled RoPE blocks
-  int turn = 0;
   for (int blk = al ? nvb : 0; blk < kb + tb; ++blk) {
     BlockList& l = out[out[0].n <= out[1].n ? 0 : 1];
-    (void)turn;
     if (l.n >= MAXB) return false;
     if (blk < kb) { l.col[l.n] = blk * 64; l.src[l.n] = 0; }
     else { l.col[l.n] = (blk - kb) * 64; l.src[l.n] = 1; }
@@ -536,6 +620,11 @@ bool latent_pair_plan(const xkv_decode_params& p, LatentTcPlan* pl) {
   off += align_up((size_t)p.batch * p.num_heads * best_s * p.v_rank * sizeof(float), 256);
   pl->off_lse = off;
   off += align_up((size_t)p.batch * p.num_heads * best_s * sizeof(float), 256);
+  pl->off_olat = 0;
+  if (p.v_proj && p.vp_sb == 0 && batched_projection_fits(p.batch, p.v_rank)) {
+    pl->off_olat = off;
+    off += align_up((size_t)p.batch * p.num_heads * p.v_rank * sizeof(float), 256);
+  }
   pl->total_bytes = off;
   return true;
 }
@@ -558,7 +647,11 @@ int latent_pair_decode(const xkv_decode_params& p, const LatentTcPlan& pl, void*
   int* status = reinterpret_cast<int*>(w);
   sm100::clear_status_kernel<<<1, 64, 0, st>>>(status);
   void* qeff = w + pl.off_qeff;
-  int rc = launch_absorb_query_lowp(p, qeff, dk, st);
+  // a projection shared by the batch is folded into the queries one matrix strip at a time (each matrix
+  // element read once per 16 batch rows); per-batch projections go row by row
+  int rc = (p.k_proj && p.kp_sb == 0 && batched_projection_fits(p.batch, p.head_dim))
+               ? launch_absorb_query_batched(p, qeff, dk, st)
+               : launch_absorb_query_lowp(p, qeff, dk, st);
   if (rc != XKV_OK) return rc;
   Args a;
   a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = p.num_heads; a.dk = dk;
@@ -575,6 +668,14 @@ int latent_pair_decode(const xkv_decode_params& p, const LatentTcPlan& pl, void*
   rc = p.dtype == XKV_BF16 ? launch<__nv_bfloat16>(tK, tKt, tV, a, head_blocks, st)
                            : launch<__half>(tK, tKt, tV, a, head_blocks, st);
   if (rc != XKV_OK) return rc;
+  if (pl.off_olat != 0) {
+    // merge the splits in latent space (fp32), then apply the shared value projection batched over the rows
+    float* o_lat = reinterpret_cast<float*>(w + pl.off_olat);
+    rc = launch_merge(a.partial_o, a.lse, o_lat, XKV_F32, p.batch, p.num_heads, pl.num_splits, p.v_rank, p.v_rank, nullptr, 1,
+                      0, 0, 0, 0, (int64_t)p.num_heads * p.v_rank, p.v_rank, st, 0, 0, p.lse_out, p.lse_sb);
+    if (rc != XKV_OK) return rc;
+    return launch_value_projection_batched(o_lat, p, st);
+  }
   return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, p.v_rank, p.value_dim,
                       p.v_proj, p.v_proj ? p.v_proj_heads : 1, p.vp_sb, p.vp_sh, p.vp_sr, p.vp_sd, p.o_sb, p.o_sh, st, 0, 0,
                       p.lse_out, p.lse_sb);

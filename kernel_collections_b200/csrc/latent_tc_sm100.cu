@@ -571,6 +571,7 @@ bool latent_tc_plan(const xkv_decode_params& pin, LatentTcPlan* pl) {
   off += align_up((size_t)p.batch * p.num_heads * best_s * p.v_rank * sizeof(float), 256);
   pl->off_lse = off;
   off += align_up((size_t)p.batch * p.num_heads * best_s * sizeof(float), 256);
+  pl->off_olat = 0;
   pl->total_bytes = off;
   return true;
 }
@@ -667,6 +668,7 @@ bool latent_pv_plan(const xkv_decode_params& p, int heads, LatentTcPlan* pl) {
   off += align_up((size_t)p.batch * heads * best_s * p.v_rank * sizeof(float), 256);
   pl->off_lse = off;
   off += align_up((size_t)p.batch * heads * best_s * sizeof(float), 256);
+  pl->off_olat = 0;
   pl->total_bytes = off;
   return true;
 }

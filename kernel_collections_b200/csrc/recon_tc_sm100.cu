@@ -84,6 +84,7 @@ struct Args {
   int* status;
   int b_batched;
   const int32_t* kv_lens;   // per-row lengths (ragged batches) or NULL
+  int drop_load;            // fault-test build only: the producer announces one stage and does not load it
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -302,6 +303,13 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
               goto producer_done;
             }
             const uint32_t sa = base + OFF_STAGE + stage * STAGE_SZ;
+#ifdef XKV_FAULT_TEST
+            if (!PAIR && a.drop_load && tile == tile_begin && c == 1 && kb == 0) {
+              mbar_expect_tx(bar_full(stage), STAGE_BYTES);     // announced, never loaded: the consumer's wait runs out
+              if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
+              continue;
+            }
+#endif
             if (PAIR) {
               // bytes of both CTAs are counted on the leader's barrier, which the leader arms for both
               const uint32_t lead_full = map_to_cta(bar_full(stage), 0);
@@ -922,6 +930,10 @@ int recon_tc_group_decode(const xkv_decode_params* layers, int n, const ReconTcP
   a.status = status;
   a.b_batched = b_batched;
   a.kv_lens = p.kv_lens;
+  a.drop_load = 0;
+#ifdef XKV_FAULT_TEST
+  a.drop_load = (p.flags & XKV_FLAG_TEST_DROP_LOAD) ? 1 : 0;
+#endif
 
   int rc;
 #define XKV_TC(T, GG) rc = lo ? launch<T, GG, true>(maps, a, pl.pair != 0, st) : launch<T, GG, false>(maps, a, pl.pair != 0, st)

@@ -9,7 +9,15 @@ namespace xkv {
 namespace sm100 {
 
 constexpr uint32_t MAX_POLLS = 1u << 26;
+#ifdef XKV_FAULT_TEST
+// Test-only build (libxkv_faulttest.so): waits give up after 20 ms, and a flag bit makes the key
+// reconstruction kernel's producer leave one announced load out, so that the time-out path (abort flag,
+// status words, drain, tensor-memory release) can be exercised without faulting or hanging the GPU.
+constexpr uint64_t WAIT_LIMIT_NS = 20000000ull;
+#define XKV_FLAG_TEST_DROP_LOAD 0x80000000u
+#else
 constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;   // a wait that lasts a second has failed
+#endif
 
 // status words at the start of every workspace
 enum { ST_CODE = 0, ST_ROLE = 1, ST_TILE = 2, ST_CHUNK = 3, ST_EXTRA = 4 };
@@ -129,6 +137,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 

@@ -91,6 +91,7 @@ struct LatentTcPlan {
   int heads_per_cta, stages, num_splits, tiles;
   size_t smem_bytes;
   size_t off_qeff, off_partial, off_lse, total_bytes;
+  size_t off_olat;     // fp32 merged latent rows in front of a batched value projection (0: unused)
 };
 bool latent_tc_supported(const xkv_decode_params& p);
 bool latent_tc_plan(const xkv_decode_params& p, LatentTcPlan* plan);
@@ -104,6 +105,11 @@ int latent_pv_run(const xkv_decode_params& p, int heads, const LatentTcPlan& pla
 
 // prologue shared by the shared-latent kernels: q_eff[b, h, :] = q . k_proj^T (or q) | q_tail, in the working dtype
 int launch_absorb_query_lowp(const xkv_decode_params& p, void* qeff, int dk, cudaStream_t st);
+
+// projections batched over the batch rows, for matrices shared by the batch (projections.cu)
+bool batched_projection_fits(int batch, int in_dim);
+int launch_absorb_query_batched(const xkv_decode_params& p, void* qeff, int dk, cudaStream_t st);
+int launch_value_projection_batched(const float* o_lat, const xkv_decode_params& p, cudaStream_t st);
 
 // ---- shared-latent decode on tcgen05, two CTAs per tile (latent_pair_sm100.cu) -------------------
 bool latent_pair_supported(const xkv_decode_params& p);

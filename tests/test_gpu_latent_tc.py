@@ -153,7 +153,8 @@ def test_cta_pair_kernel_against_oracle_and_mma_sync_kernel(dtype, case):
     qr = (torch.randn(b, H, rope, generator=g) / 3).to(dtype) if rope else None
     kr = (torch.randn(b, L, rope, generator=g) / 3).to(dtype) if rope else None
     dev = lambda x: None if x is None else x.to(DEV)
-    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT, q=dev(qn), k=dev(c), v=dev(c)[..., :Rv], q_tail=dev(qr),
+    cd = dev(c)                                  # values are a prefix of the key latent: one tensor, read once
+    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT, q=dev(qn), k=cd, v=cd[..., :Rv], q_tail=dev(qr),
               k_tail=dev(kr), sm_scale=0.3, num_kv_heads=1)
     assert ops.plan(**kw) == "latent_pair"
     got = ops.decode(entry="xkv_mla_decode", **kw)
@@ -177,7 +178,8 @@ def test_cta_pair_kernel_against_oracle_and_mma_sync_kernel(dtype, case):
         cp[i, n:] = float("nan")
         if krp is not None:
             krp[i, n:] = float("nan")
-    kwr = dict(kw, k=dev(cp), v=dev(cp)[..., :Rv], k_tail=dev(krp), kv_lens=torch.tensor(lens, dtype=torch.int32, device=DEV))
+    cpd = dev(cp)
+    kwr = dict(kw, k=cpd, v=cpd[..., :Rv], k_tail=dev(krp), kv_lens=torch.tensor(lens, dtype=torch.int32, device=DEV))
     got_r = ops.decode(entry="xkv_mla_decode", **kwr)
     status_ok()
     for i, n in enumerate(lens):
@@ -187,9 +189,34 @@ def test_cta_pair_kernel_against_oracle_and_mma_sync_kernel(dtype, case):
     u = torch.nn.functional.normalize(torch.randn(lora, generator=g), dim=0)
     q2 = (3.0 * u + 0.05 * torch.randn(b, H, lora, generator=g)).to(dtype)
     c2 = ((torch.arange(L, dtype=torch.float32) / 48.0 * 9.0)[None, :, None] * u + 0.05 * torch.randn(b, L, lora, generator=g)).to(dtype)
-    kw2 = dict(kw, q=dev(q2), k=dev(c2), v=dev(c2)[..., :Rv], sm_scale=0.4)
+    c2d = dev(c2)
+    kw2 = dict(kw, q=dev(q2), k=c2d, v=c2d[..., :Rv], sm_scale=0.4)
     got2 = ops.decode(entry="xkv_mla_decode", **kw2)
     status_ok()
     close(got2, torch.matmul(torch.softmax((torch.matmul(q2.float(), c2.float().transpose(-1, -2))
                                             + (0 if qr is None else torch.matmul(qr.float(), kr.float().transpose(-1, -2)))) * 0.4, -1),
                              c2.float()[..., :Rv]), "latent_pair with climbing logits")
+
+
+@pytest.mark.parametrize("case", [(2, 64, 256, 0, 900, 256), (1, 96, 256, 64, 400, 128)])
+def test_cta_pair_kernel_with_a_separate_value_latent(case):
+    """Key latent and value latent as two tensors (absorbed factorized cache with 64 or more heads): the
+    pair splits the value columns and deals the key blocks out between its CTAs."""
+    b, H, rk, rope, L, Rv = case
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(45)
+    qn = (torch.randn(b, H, rk, generator=g) / 3).to(dtype)
+    Ak = (torch.randn(b, L, rk, generator=g) / 3).to(dtype)
+    Av = torch.randn(b, L, Rv, generator=g).to(dtype)
+    qr = (torch.randn(b, H, rope, generator=g) / 3).to(dtype) if rope else None
+    kr = (torch.randn(b, L, rope, generator=g) / 3).to(dtype) if rope else None
+    dev = lambda x: None if x is None else x.to(DEV)
+    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT, q=dev(qn), k=dev(Ak), v=dev(Av), q_tail=dev(qr),
+              k_tail=dev(kr), sm_scale=0.3, num_kv_heads=1)
+    assert ops.plan(**kw) == "latent_pair"
+    got = ops.decode(entry="xkv_mla_decode", **kw)
+    status_ok()
+    s = torch.matmul(qn.float(), Ak.float().transpose(-1, -2))
+    if rope:
+        s = s + torch.matmul(qr.float(), kr.float().transpose(-1, -2))
+    close(got, torch.matmul(torch.softmax(s * 0.3, -1), Av.float()), "latent_pair, separate value latent")
