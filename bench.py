@@ -43,7 +43,8 @@ UNIT = "tokens/s"
 # (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured launch; the
 # traffic of these streaming kernels grows in proportion to the rows processed).  profiles/ has the captures.
 DRAM_PER_ALGORITHMIC_BYTE = {
-    "recon_tc": (1.020, "profiles/recon_tc_kernel_c2_context4096.md"),
+    "recon_tc": (1.03, "profiles/recon_tc_kernel_c5_and_c2_cutdown.md"),
+    "latent_pair": (1.03, "profiles/latent_pair_kernel_c4_cutdown.md"),
     "dense_tc": (1.004, "profiles/dense_tc_and_latent_tc_kernels_quarter_context.md"),
     "latent_tc": (1.063, "profiles/dense_tc_and_latent_tc_kernels_quarter_context.md"),
 }
