@@ -163,7 +163,9 @@ XKV_API int xkv_decode(const xkv_decode_params* p, void* workspace, size_t works
  *    returns XKV_ERR_SCRATCH_LIMIT and launches nothing (lower num_splits or the batch, or use
  *    xkv_decode() with a workspace).  The tensor-core kernels are not used on this path.
  *  - The first call on each device resolves the array's device address (cudaGetSymbolAddress,
- *    with that device current).  Make that first call outside any stream capture.
+ *    with that device current) and keeps it for the life of the process.  Make that first call
+ *    outside any stream capture.  The kept address does not survive a cudaDeviceReset of that
+ *    device: a process that resets a device must not call this entry point on it afterwards.
  *  - All calls on one device share the one array, which keeps whatever the last call left in
  *    it; every call rewrites what it later reads, so stale contents are harmless, but two
  *    calls that overlap on the GPU (different streams, or concurrent host threads) race on
