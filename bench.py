@@ -259,8 +259,7 @@ class Group(Workload):
     def step(self, *over):
         import kernel_collections_b200 as K
         if self.v_only:
-            outs = [K.group_query_attention_factorized_v_only(self.q[i], self.Ks[i].transpose(1, 2), self.Av, self.Bv4[i])
-                    for i in range(self.NL)]
+            outs = K.xkv_group_decode_v_only(self.q, [k.transpose(1, 2) for k in self.Ks], self.Av, self.Bvs)
         else:
             outs = K.xkv_group_decode(self.q, self.A, self.Bs, self.Av, self.Bvs, theta=self.theta)
         return torch.stack(outs, dim=1)          # (b, NL, H, 1, D)

@@ -17,6 +17,7 @@ from .attention import (  # noqa: F401
     rope_query,
     latent_append,
     xkv_group_decode,
+    xkv_group_decode_v_only,
     mla_absorbed_decode,
 )
 from . import flash_recontruction, flash_decoding  # noqa: F401

@@ -306,6 +306,18 @@ def xkv_group_decode(queries, key_A, key_Bs, value, value_Bs=None, *, theta, sm_
     return [o.unsqueeze(2) for o in ops.group_decode(layers)]
 
 
+def xkv_group_decode_v_only(queries, keys, value_A, value_Bs, *, sm_scale=None, kv_lens=None):
+    """Cross-layer group of the V-only-factorized form: every layer has its own dense keys
+    (bsz, KVH, L, D) and value projection, all layers share one value latent value_A (bsz, L, Rv).  Per
+    layer this is attention.py:202-274; as a group the shared latent is streamed ONCE, with the heads of
+    all layers stacked for the softmax + P.A_v pass.  Returns a list of (bsz, H, 1, D)."""
+    D = queries[0].shape[-1]
+    scale = D ** -0.5 if sm_scale is None else sm_scale
+    layers = [dict(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_LATENT, q=_q3(q), k=keys[i].transpose(1, 2), v=value_A,
+                   v_proj=as_key_proj(value_Bs[i], D), sm_scale=scale, kv_lens=kv_lens) for i, q in enumerate(queries)]
+    return [o.unsqueeze(2) for o in ops.group_decode(layers)]
+
+
 def mla_absorbed_decode(q_nope, q_rope, c_kv, k_rope, W_uk, W_uv, sm_scale, *, kv_lens=None):
     """MLA absorbed decode.  q_nope (b,H,nope); q_rope (b,H,rope); c_kv (b,L,lora);
     k_rope (b,L,rope); W_uk (H,nope,lora); W_uv (H,lora,v) -> (b,H,v).  W_uk is folded into q,

@@ -159,8 +159,19 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap tmV, const Args a) {
     float m_ref = -CUDART_INF_F;                             // reference maximum the exponentials use
     float l_sum = 0.f;
     float cur[TK], nxt[TK];
+    // a row's 64 logits of a tile: 16-byte loads when the row is aligned and the tile lies inside the row
+    const bool vec_ok = (a.lg_sh % 4 == 0) && (a.lg_sb % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.logits) & 15u) == 0);
     auto fetch = [&](int tile, float (&dst)[TK]) {
       const int t0 = tile * TK;
+      if (vec_ok && live && tile < tile_end && t0 + TK <= row_len) {
+        const float4* src = reinterpret_cast<const float4*>(lrow + t0);
+#pragma unroll
+        for (int i = 0; i < TK / 4; ++i) {
+          const float4 v = __ldg(src + i);
+          dst[4 * i] = v.x * LOG2E; dst[4 * i + 1] = v.y * LOG2E; dst[4 * i + 2] = v.z * LOG2E; dst[4 * i + 3] = v.w * LOG2E;
+        }
+        return;
+      }
 #pragma unroll
       for (int i = 0; i < TK; ++i) {
         const int tk = t0 + i;

@@ -191,3 +191,24 @@ def test_factorized_keys_with_dense_values(dtype, case):
     for i, n in enumerate(lens):
         close(got_r[i:i + 1], O.xkv_fused_k_only(q[i:i + 1], A[i:i + 1, :n], Bk[i:i + 1], V[i:i + 1, :n], sm_scale=D ** -0.5),
               f"k_only ragged row {i}")
+
+
+def test_v_only_group_streams_the_shared_latent_once():
+    """Four layers with their own dense keys and one shared value latent as ONE group call (the heads of all
+    layers stacked for the value pass): every layer against the oracle and against its single-layer call."""
+    NL, b, H, kvh, L, Rv = 4, 2, 32, 8, 900, 256
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(58)
+    qs = [torch.randn(b, H, 1, D, generator=g).to(dtype) for _ in range(NL)]
+    ks = [torch.randn(b, kvh, L, D, generator=g).to(dtype) for _ in range(NL)]
+    Av = torch.randn(b, L, Rv, generator=g).to(dtype)
+    Bvs = [(torch.randn(Rv, kvh * D, generator=g) / Rv ** 0.5).to(dtype) for _ in range(NL)]
+    Avd = Av.to(DEV)
+    got = K.xkv_group_decode_v_only([x.to(DEV) for x in qs], [x.to(DEV) for x in ks], Avd, [x.to(DEV) for x in Bvs])
+    rc, detail = _C.last_status(torch.device(DEV))
+    assert rc == 0, detail
+    for i in range(NL):
+        Bv4 = b4(Bvs[i], b).contiguous()
+        close(got[i], O.gqa_factorized_v_only(qs[i], ks[i], Av, Bv4), f"v-only group layer {i}")
+        single = K.group_query_attention_factorized_v_only(qs[i].to(DEV), ks[i].to(DEV), Avd, Bv4.to(DEV))
+        close(got[i], single.float().cpu(), f"v-only group layer {i} vs single-layer call", 4e-3, 3e-3)
