@@ -504,6 +504,9 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="batch rows per GPU (cut-down case for profiler captures)")
     ap.add_argument("--kv-len", type=int, default=0, help="context length override (cut-down case)")
     ap.add_argument("--pair", default="auto", choices=["auto", "on", "off"], help="key reconstruction: CTA-pair kernel")
+    ap.add_argument("--gather", default="auto", choices=["auto", "nccl", "peer"],
+                    help="N > 1: how the outputs are gathered.  peer = the library's peer-store kernel over symmetric memory; "
+                         "auto = peer for steps under 2 ms when it can be set up and agrees with NCCL, else NCCL")
     ap.add_argument("--parity-rows", type=int, default=2, help="batch rows checked against the CPU oracle (0 = skip)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the oracle legs (parity and CPU baseline)")
     ap.add_argument("--no-e2e", action="store_true")
@@ -564,10 +567,42 @@ def main():
     gather_dim = 1 if (args.workload == "c4" and args.shard == "heads") else 0
     total_gather = (wl.H if gather_dim == 1 else wl.b * world) if world > 1 else 0
 
+    # how the outputs come together at N > 1: NCCL all-gather, or the library's peer-store kernel (batch shards only)
+    peer_gather, gather_kind = None, "nccl"
+    if world > 1 and gather_dim == 0 and args.gather in ("auto", "peer"):
+        def all_ranks(flag: bool) -> bool:                    # every rank takes the same branch
+            t = torch.tensor([1 if flag else 0], device=dev)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
+            return bool(int(t.item()))
+
+        probe = wl.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(3):
+            wl.step()
+        torch.cuda.synchronize()
+        if all_ranks(args.gather == "peer" or (time.perf_counter() - t0) / 3 < 2e-3):
+            pg = None
+            try:
+                pg = xdist.PeerAllGather(tuple(probe.shape), probe.dtype, dev)
+            except Exception as e:        # symmetric memory not available here: the collective stays
+                sys.stderr.write(f"peer gather not used: {e!r}\n")
+            if all_ranks(pg is not None):
+                same = torch.equal(pg(probe), xdist.all_gather_outputs(probe, total_gather)) and pg.status()[0] == 0
+                if all_ranks(same):
+                    peer_gather, gather_kind = pg, "peer stores (xkv_peer_allgather)"
+    if world > 1:
+        config["parallelism"] = config["parallelism"].replace("NCCL all-gather of outputs", f"all-gather of outputs by {gather_kind}")
+
+    def gather(o):
+        if peer_gather is not None:
+            return peer_gather(o)
+        return xdist.all_gather_outputs(o if gather_dim == 0 else o.contiguous(), total_gather, dim=gather_dim)
+
     def step():
         o = wl.step()
         if world > 1:
-            o = xdist.all_gather_outputs(o if gather_dim == 0 else o.contiguous(), total_gather, dim=gather_dim)
+            o = gather(o)
         return o
 
     def barrier():
@@ -600,12 +635,12 @@ def main():
         local = wl.step()
         local = local if gather_dim == 0 else local.contiguous()
         for _ in range(3):
-            xdist.all_gather_outputs(local, total_gather, dim=gather_dim)
+            gather(local)
         barrier()
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         g0.record(stream)
         for _ in range(20):
-            xdist.all_gather_outputs(local, total_gather, dim=gather_dim)
+            gather(local)
         g1.record(stream)
         barrier()
         gather_ms = g0.elapsed_time(g1) / 20
@@ -721,6 +756,7 @@ def main():
             "gpu_launches": wl.launches * args.steps, "roofline": roof}
     if world > 1:
         line["all_gather_ms"] = gather_ms
+        line["all_gather"] = gather_kind
     if parity is not None:
         line["parity"] = parity
     if cpu_baseline is not None:

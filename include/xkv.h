@@ -261,6 +261,21 @@ XKV_API int xkv_latent_append(const void* x, int64_t x_sb, const void* proj, int
                       void* latent, int64_t l_sb, int64_t l_sl, const int32_t* positions, int position,
                       int dtype, int batch, int in_dim, int rank, int capacity, void* stream);
 
+/*
+ * All-gather of per-rank output shards with plain peer stores over NVLink (no collective library), for
+ * steps short enough that a collective's latency shows.  bufs[r] (r < world) is rank r's gather buffer as
+ * mapped in THIS process (symmetric / peer-mapped memory of one layout: 2 halves x world slots x
+ * shard_bytes, then `world` uint32 flag words at flags_offset, zero before the first call).  The launch copies
+ * `local` into slot `rank` of half (epoch & 1) of every rank's buffer, publishes `epoch` in every rank's
+ * flag word `rank`, and returns (on the stream) once this rank's own flag words all show `epoch`: its
+ * half then holds every rank's shard.  `epoch` must grow by one per call on every rank, starting at 1.  A
+ * peer that does not show up within a second leaves XKV_ERR_TIMEOUT in status_dev[0] (role 40, peer,
+ * epoch in [1..3]) instead of hanging.  The reference has no multi-GPU code; this replaces the
+ * all_gather_into_tensor the batch-sharded decode ends with.
+ */
+XKV_API int xkv_peer_allgather(const void* local, size_t shard_bytes, void* const* bufs, size_t flags_offset, int rank,
+                       int world, uint32_t epoch, int* status_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -26,7 +26,7 @@ EXPORTS = [
     "xkv_workspace_status", "xkv_decode_builtin_scratch",
     "xkv_dense_decode", "xkv_absorbed_decode", "xkv_recon_rope_decode", "xkv_qab_logits",
     "xkv_mla_decode", "xkv_group_decode_workspace_bytes", "xkv_group_decode", "xkv_merge",
-    "xkv_rope_table", "xkv_rope_query", "xkv_latent_append",
+    "xkv_rope_table", "xkv_rope_query", "xkv_latent_append", "xkv_peer_allgather",
 ]
 
 
@@ -110,6 +110,9 @@ def load():
         lib.xkv_latent_append.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64,
                                           C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_void_p]
+        lib.xkv_peer_allgather.restype = C.c_int
+        lib.xkv_peer_allgather.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_size_t, C.c_int, C.c_int,
+                                           C.c_uint32, C.c_void_p, C.c_void_p]
         lib.xkv_decode_params_size.restype = C.c_size_t
         lib.xkv_decode_builtin_scratch.restype = C.c_int
         lib.xkv_decode_builtin_scratch.argtypes = [C.POINTER(DecodeParams), C.c_void_p]

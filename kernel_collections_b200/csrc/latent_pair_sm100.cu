@@ -49,6 +49,7 @@ static_assert(OFF_RING % 1024 == 0 && BLK % 1024 == 0 && OFF_P % 1024 == 0, "swi
 constexpr float RESCALE_THRESHOLD = 8.f;
 constexpr uint32_t S_COL0 = 256;             // tensor-memory columns: O in 0..255, three score buffers of 32 from 256
 constexpr int SBUF = 3;
+constexpr bool kSplitOddBlock = false;      // (measured: sharing the odd block between the CTAs is 9 % slower, see make_lists)
 
 // The 64-column blocks one CTA of the pair works on.  Blocks [0, nv) are its own value columns (in
 // alias mode they are score blocks too); blocks with score[i] set take part in S.
@@ -57,6 +58,7 @@ struct BlockList {
   int col[MAXB];        // column (elements) inside the tensor the block is loaded from
   int src[MAXB];        // 0: key latent, 1: decoupled RoPE key part, 2: value latent
   int qcol[MAXB];       // matching column of the effective query, or -1 when the block is values only
+  int k4_lo[MAXB], k4_hi[MAXB];   // which of the block's four 16-column MMA steps this CTA scores: [lo, hi)
 };
 
 struct Args {
@@ -241,23 +243,31 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       const uint32_t idesc_s = (1u << 4) | (kfmt << 7) | (kfmt << 10) | (((uint32_t)T >> 3) << 17) | ((128u >> 4) << 24);
       const uint32_t idesc_o = (1u << 4) | (kfmt << 7) | (kfmt << 10) | (1u << 16) | (((uint32_t)nvc >> 3) << 17) |
                                ((128u >> 4) << 24);
+      // operand descriptors built once; the loops only add offsets
+      const uint64_t dq0 = smem_desc(base + OFF_Q, 16, 1024), dk0 = smem_desc(base + OFF_RING, 16, 1024);
+      const uint64_t dp0 = smem_desc(base + OFF_P, 16, 1024), dv0 = smem_desc(base + OFF_RING, BLK, 1024);
       auto issue_scores = [&](int i) -> bool {
         const int stage = i % STAGES, sb = i % SBUF;
         if (i >= SBUF && !XKV_LP_WAIT(1, true, mbar_wait(bar_sempty(sb), ((uint32_t)(i / SBUF) & 1u) ^ 1u, abort_flag))) return false;
         if (!XKV_LP_WAIT(2, true, mbar_wait(bar_full(stage), (uint32_t)(i / STAGES) & 1u, abort_flag))) return false;
         tc_fence_after();
-        const uint32_t ss = base + OFF_RING + stage * (MAXB * BLK);
         const uint32_t tacc = tmem_base + S_COL0 + (uint32_t)sb * (uint32_t)T;
         int qi = 0;
         bool first = true;
         for (int k = 0; k < bl.n; ++k) {
           if (bl.qcol[k] < 0) continue;
+          const uint64_t da_b = desc_advance(dq0, (uint32_t)(qi * QBLK));
+          const uint64_t db_b = desc_advance(dk0, (uint32_t)(stage * (MAXB * BLK) + k * BLK));
+          if (bl.k4_lo[k] == 0 && bl.k4_hi[k] == 4) {
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            const uint64_t da = smem_desc(base + OFF_Q + qi * QBLK + k4 * 32, 16, 1024);
-            const uint64_t db = smem_desc(ss + k * BLK + k4 * 32, 16, 1024);
-            tc_mma(tacc, da, db, idesc_s, first ? 0u : 1u);
+            for (int k4 = 0; k4 < 4; ++k4)
+              tc_mma(tacc, desc_advance(da_b, k4 * 32), desc_advance(db_b, k4 * 32), idesc_s, (first && k4 == 0) ? 0u : 1u);
             first = false;
+          } else {
+            for (int k4 = bl.k4_lo[k]; k4 < bl.k4_hi[k]; ++k4) {
+              tc_mma(tacc, desc_advance(da_b, k4 * 32), desc_advance(db_b, k4 * 32), idesc_s, first ? 0u : 1u);
+              first = false;
+            }
           }
           ++qi;
         }
@@ -273,13 +283,10 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         if (!ok) break;
         if (!XKV_LP_WAIT(3, true, mbar_wait(bar_pfull, (uint32_t)i & 1u, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        const uint32_t ss = base + OFF_RING + (i % STAGES) * (MAXB * BLK);
+        const uint64_t dv_st = desc_advance(dv0, (uint32_t)((i % STAGES) * (MAXB * BLK)));
 #pragma unroll
-        for (int k4 = 0; k4 < T / 16; ++k4) {
-          const uint64_t da = smem_desc(base + OFF_P + k4 * 32, 16, 1024);
-          const uint64_t db = smem_desc(ss + k4 * 2048, BLK, 1024);
-          tc_mma(tmem_base, da, db, idesc_o, (i == 0 && k4 == 0) ? 0u : 1u);
-        }
+        for (int k4 = 0; k4 < T / 16; ++k4)
+          tc_mma(tmem_base, desc_advance(dp0, k4 * 32), desc_advance(dv_st, k4 * 2048), idesc_o, (i == 0 && k4 == 0) ? 0u : 1u);
         tc_commit(bar_empty(i % STAGES));      // the tile's blocks and ...
         tc_commit(bar_pempty);                 // ... the P buffer are free once these MMAs have run
       }
@@ -534,13 +541,26 @@ bool make_lists(const xkv_decode_params& p, BlockList out[2]) {
   }
   // score blocks not covered above: all key blocks (separate value latent) or the key blocks past the
   // value columns (alias), then the decoupled RoPE blocks
-  for (int blk = al ? nvb : 0; blk < kb + tb; ++blk) {
-    BlockList& l = out[out[0].n <= out[1].n ? 0 : 1];
+  for (int r = 0; r < 2; ++r)
+    for (int i = 0; i < MAXB; ++i) { out[r].k4_lo[i] = 0; out[r].k4_hi[i] = 4; }
+  auto put = [&](BlockList& l, int blk, int lo, int hi) {
     if (l.n >= MAXB) return false;
     if (blk < kb) { l.col[l.n] = blk * 64; l.src[l.n] = 0; }
     else { l.col[l.n] = (blk - kb) * 64; l.src[l.n] = 1; }
     l.qcol[l.n] = blk * 64;
+    l.k4_lo[l.n] = lo; l.k4_hi[l.n] = hi;
     ++l.n;
+    return true;
+  };
+  const int first_extra = al ? nvb : 0, extras = kb + tb - first_extra;
+  for (int blk = first_extra; blk < kb + tb; ++blk) {
+    // an odd block out (MLA: the decoupled RoPE block) is loaded by both CTAs and each scores half of its
+    // MMA steps, so both issue the same number of score MMAs per tile
+    if (kSplitOddBlock && blk == kb + tb - 1 && (extras & 1) && out[0].n == out[1].n) {
+      if (!put(out[0], blk, 0, 2) || !put(out[1], blk, 2, 4)) return false;
+    } else if (!put(out[out[0].n <= out[1].n ? 0 : 1], blk, 0, 4)) {
+      return false;
+    }
   }
   // each CTA must score at least one block (its score buffer is exchanged every tile)
   for (int r = 0; r < 2; ++r) {
@@ -668,6 +688,8 @@ int latent_pair_decode(const xkv_decode_params& p, const LatentTcPlan& pl, void*
   rc = p.dtype == XKV_BF16 ? launch<__nv_bfloat16>(tK, tKt, tV, a, head_blocks, st)
                            : launch<__half>(tK, tKt, tV, a, head_blocks, st);
   if (rc != XKV_OK) return rc;
+  if (pl.off_olat != 0 && pl.num_splits == 1 && !p.lse_out)   // one split: its normalised partial IS the latent output
+    return launch_value_projection_batched(a.partial_o, p, st);
   if (pl.off_olat != 0) {
     // merge the splits in latent space (fp32), then apply the shared value projection batched over the rows
     float* o_lat = reinterpret_cast<float*>(w + pl.off_olat);

@@ -121,22 +121,22 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap tmV, const Args a) {
       int stage = 0, pbuf = 0;
       uint32_t vph = 0, pph = 0;
       bool first = true;
+      // operand descriptors built once; the loop only adds offsets
+      const uint64_t dp0 = smem_desc(base + OFF_P, 16, 1024), dv0 = smem_desc(base + OFF_V, BOX_BYTES, 1024);
       for (int tile = tile_begin; tile < tile_end; ++tile) {
         if (!mbar_wait(bar_pfull(pbuf), pph, abort_flag) || !mbar_wait(bar_vfull(stage), vph, abort_flag)) {
           report(a.status, XKV_ERR_TIMEOUT, 21, tile, cb, b);
           goto mma_done;
         }
         tc_fence_after();
-        const uint32_t sp = base + OFF_P + pbuf * P_BYTES, sv = base + OFF_V + stage * STAGE_BYTES;
+        const uint64_t da_b = desc_advance(dp0, (uint32_t)(pbuf * P_BYTES));           // P: K-major
+        const uint64_t db_b = desc_advance(dv0, (uint32_t)(stage * STAGE_BYTES));      // V: MN-major
 #pragma unroll
         for (int k4 = 0; k4 < TK / 16; ++k4) {
-          const uint64_t da = smem_desc(sp + k4 * 32, 16, 1024);                       // P: K-major
-          const uint64_t db0 = smem_desc(sv + k4 * 2048, BOX_BYTES, 1024);             // V: MN-major
-          tc_mma(tmem_base, da, db0, id0, (first && k4 == 0) ? 0u : 1u);
-          if (n1 > 0) {
-            const uint64_t db1 = smem_desc(sv + 4 * BOX_BYTES + k4 * 2048, BOX_BYTES, 1024);
-            tc_mma(tmem_base + 256u, da, db1, id1, (first && k4 == 0) ? 0u : 1u);
-          }
+          const uint64_t da = desc_advance(da_b, k4 * 32);
+          tc_mma(tmem_base, da, desc_advance(db_b, k4 * 2048), id0, (first && k4 == 0) ? 0u : 1u);
+          if (n1 > 0)
+            tc_mma(tmem_base + 256u, da, desc_advance(db_b, 4 * BOX_BYTES + k4 * 2048), id1, (first && k4 == 0) ? 0u : 1u);
         }
         first = false;
         tc_commit(bar_vempty(stage));       // the value tile and ...

@@ -339,6 +339,9 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
                              ((256u >> 3) << 17) | (((PAIR ? 256u : 128u) >> 4) << 24);
       int stage = 0, abuf = 0;
       uint32_t phase = 0, aphase = 0;
+      // operand descriptors of stage 0, built once; the loops only add offsets
+      const uint64_t da0 = smem_desc(base + OFF_STAGE, 16, 1024);
+      const uint64_t db0 = smem_desc(base + OFF_STAGE + A_BYTES, B_BOX, 1024);
       for (int tile = tile_begin; tile < tile_end; tile += TSTEP) {
         for (int c = 0; c < NCH; ++c) {
           if (!XKV_PROF_WAIT(1, mbar_wait(bar_tempty(abuf), aphase ^ 1u, abort_flag))) {
@@ -353,11 +356,12 @@ recon_tc_kernel(const __grid_constant__ TensorMaps maps, const Args a) {
               goto mma_done;
             }
             tc_fence_after();
-            const uint32_t sa = base + OFF_STAGE + stage * STAGE_SZ;
+            const uint64_t da_st = desc_advance(da0, (uint32_t)(stage * STAGE_SZ));
+            const uint64_t db_st = desc_advance(db0, (uint32_t)(stage * STAGE_SZ));
 #pragma unroll
             for (int k4 = 0; k4 < BK / 16; ++k4) {
-              const uint64_t da = smem_desc(sa + k4 * 32, 16, 1024);
-              const uint64_t db = smem_desc(sa + A_BYTES + k4 * 2048, B_BOX, 1024);
+              const uint64_t da = desc_advance(da_st, k4 * 32);
+              const uint64_t db = desc_advance(db_st, k4 * 2048);
               if (PAIR) tc_mma_pair(tacc, da, db, idesc, (kb | k4) != 0 ? 1u : 0u);
               else tc_mma(tacc, da, db, idesc, (kb | k4) != 0 ? 1u : 0u);
             }

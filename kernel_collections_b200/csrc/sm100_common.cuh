@@ -155,6 +155,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
+// The descriptor of the same layout `bytes` further on in shared memory (a multiple of 16; the 14-bit address
+// field counts 16-byte units and no offset used here carries out of it).  The one thread that issues the
+// MMAs builds its descriptors once and only adds offsets in its loops: every instruction it spends per MMA
+// is issue time the tensor core waits for.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "

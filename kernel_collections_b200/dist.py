@@ -83,3 +83,77 @@ def head_sharded_decode(local_op: Callable[..., torch.Tensor], head_tensors: Seq
     local = local_op(*shards, *args, **kwargs)
     total = head_tensors[0].shape[head_dims[0]]
     return all_gather_outputs(local, total, group=group, dim=out_head_dim)
+
+
+class PeerAllGather:
+    """All-gather of equal per-rank output shards along dim 0 with the library's peer-store kernel
+    (xkv_peer_allgather) instead of a collective: one small launch per step, for decode steps short enough
+    that a collective's 30-60 us show.  The gather buffer lives in symmetric memory (every rank's copy is
+    mapped into all ranks of the box); two halves alternate between calls, so the tensor returned by call n
+    stays valid until call n + 2.
+
+    Construction is collective over `group` and raises if symmetric memory cannot be set up on this system
+    (callers then keep `all_gather_outputs`).  The host-side bookkeeping (layout, epochs, halves) is in
+    `PeerGatherPlan`, which needs no GPU."""
+
+    def __init__(self, local_shape, dtype, device, group=None):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _C
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.plan = PeerGatherPlan(local_shape, torch.empty((), dtype=dtype).element_size(), self.world)
+        self.local_shape, self.dtype, self.device = tuple(local_shape), dtype, device
+        self.buf = symm_mem.empty(self.plan.total_bytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(ptrs) != self.world or ptrs[self.rank] != self.buf.data_ptr():
+            raise RuntimeError("symmetric memory handle does not describe this group's buffers")
+        self._ptrs = (C.c_void_p * self.world)(*ptrs)
+        self._status = torch.zeros(8, dtype=torch.int32, device=device)
+        self._lib = _C.load()
+        self._check = _C.check
+        dist.barrier(group)                  # every rank's flags are zero before anyone publishes into them
+
+    def __call__(self, local: torch.Tensor) -> torch.Tensor:
+        if tuple(local.shape) != self.local_shape or local.dtype != self.dtype or not local.is_contiguous():
+            raise ValueError("local shard does not match the shape / dtype this gather was built for")
+        epoch, half_off = self.plan.next_call()
+        with torch.cuda.device(self.device):
+            rc = self._lib.xkv_peer_allgather(local.data_ptr(), self.plan.shard_bytes, self._ptrs, self.plan.flags_offset,
+                                              self.rank, self.world, epoch, self._status.data_ptr(),
+                                              torch.cuda.current_stream(self.device).cuda_stream)
+        self._check(rc, "xkv_peer_allgather")
+        out = self.buf[half_off: half_off + self.world * self.plan.shard_bytes].view(self.dtype)
+        return out.view((self.world * self.local_shape[0],) + self.local_shape[1:])
+
+    def status(self):
+        """(code, role, peer, epoch) left by a wait that gave up; (0, ...) when all peers showed up."""
+        return tuple(self._status[:4].tolist())
+
+
+class PeerGatherPlan:
+    """Layout and call bookkeeping of PeerAllGather: [2 halves][world][shard] then `world` flag words."""
+
+    def __init__(self, local_shape, elem_size: int, world: int):
+        n = 1
+        for d in local_shape:
+            n *= int(d)
+        self.shard_bytes = n * elem_size
+        if self.shard_bytes == 0 or self.shard_bytes % 16 != 0:
+            raise ValueError("a shard must be a non-empty multiple of 16 bytes")
+        if not (1 <= world <= 16):
+            raise ValueError("1 to 16 ranks")
+        self.world = world
+        self.flags_offset = 2 * world * self.shard_bytes
+        self.total_bytes = self.flags_offset + 256
+        self.epoch = 0
+
+    def next_call(self):
+        """(epoch, byte offset of the half this call fills); epochs start at 1 and alternate the halves."""
+        self.epoch += 1
+        if self.epoch >= 2 ** 32:
+            raise OverflowError("epoch counter exhausted")
+        return self.epoch, (self.epoch & 1) * self.world * self.shard_bytes

@@ -69,3 +69,29 @@ def test_sharded_decode_gloo_world2(total):
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), total, ret), nprocs=world, join=True)
     assert dict(ret) == {0: True, 1: True}
+
+
+def test_peer_gather_plan_layout_and_epochs():
+    """Host side of the peer-store all-gather: buffer layout, the alternation of the two halves, argument checks
+    (the kernel side needs GPUs that can map each other's memory)."""
+    from kernel_collections_b200.dist import PeerGatherPlan
+    p = PeerGatherPlan((16, 32, 1, 128), 2, 8)
+    assert p.shard_bytes == 16 * 32 * 128 * 2
+    assert p.flags_offset == 2 * 8 * p.shard_bytes and p.total_bytes >= p.flags_offset + 8 * 4
+    calls = [p.next_call() for _ in range(5)]
+    assert [e for e, _ in calls] == [1, 2, 3, 4, 5]
+    assert [off for _, off in calls] == [8 * p.shard_bytes, 0, 8 * p.shard_bytes, 0, 8 * p.shard_bytes]
+    with pytest.raises(ValueError):
+        PeerGatherPlan((3, 1), 2, 4)          # 6 bytes: not a multiple of 16
+    with pytest.raises(ValueError):
+        PeerGatherPlan((8,), 2, 17)
+    # the C entry point rejects what the kernel could not handle, without a GPU
+    import ctypes as C
+    from kernel_collections_b200 import _C
+    lib = _C.load()
+    ptrs = (C.c_void_p * 2)(0x1000, 0x2000)
+    assert lib.xkv_peer_allgather(None, 1024, ptrs, 4096, 0, 2, 1, None, None) == -1
+    assert lib.xkv_peer_allgather(0x4000, 1000, ptrs, 4096, 0, 2, 1, None, None) == -3      # shard not a multiple of 16
+    assert lib.xkv_peer_allgather(0x4000, 1024, ptrs, 1024, 0, 2, 1, None, None) == -1      # flags inside the data
+    assert lib.xkv_peer_allgather(0x4000, 1024, ptrs, 4096, 0, 2, 0, None, None) == -1      # epoch 0 is the empty state
+    assert lib.xkv_peer_allgather(0x4000, 1024, ptrs, 4096, 2, 2, 1, None, None) == -1      # rank out of range
