@@ -265,7 +265,8 @@ XKV_API int xkv_latent_append(const void* x, int64_t x_sb, const void* proj, int
  * All-gather of per-rank output shards with plain peer stores over NVLink (no collective library), for
  * steps short enough that a collective's latency shows.  bufs[r] (r < world) is rank r's gather buffer as
  * mapped in THIS process (symmetric / peer-mapped memory of one layout: 2 halves x world slots x
- * shard_bytes, then `world` uint32 flag words at flags_offset, zero before the first call).  The launch copies
+ * shard_bytes, then 256 bytes at flags_offset, zero before the first call: `world` uint32 flag words and, from
+ * byte 128, the kernel's own arrival counters).  The launch copies
  * `local` into slot `rank` of half (epoch & 1) of every rank's buffer, publishes `epoch` in every rank's
  * flag word `rank`, and returns (on the stream) once this rank's own flag words all show `epoch`: its
  * half then holds every rank's shard.  `epoch` must grow by one per call on every rank, starting at 1.  A

@@ -8,18 +8,22 @@
 //     split) and half of the score contraction: it keeps the matching 64-wide blocks of Q resident,
 //     streams only those blocks of the latent rows (each latent byte is fetched by exactly one of the
 //     two CTAs, so the pair reads the cache once), and forms S_r = Q_r . K_r^T on the tensor core;
-//   * the two partial score tiles are exchanged through distributed shared memory (each warp stages its
-//     share and sends it with one cp.async.bulk into the peer's buffer, which counts the bytes on the peer's
-//     mbarrier; no multicast, no fences on the sender) and added; both CTAs then
+//   * the two partial score tiles are exchanged through distributed shared memory (st.async from registers
+//     into the peer's buffer, which counts the bytes on the peer's mbarrier; no multicast, no fences on the
+//     sender) and added; both CTAs then
 //     hold the same S, run the same softmax (one thread per head row, lazily updated reference
 //     maximum as in the two-pass value kernel) and multiply their own value columns: O_r += P . V_r.
 // Warps: 0 TMA producer (4-stage ring of whole tiles), 1 MMA issuer (the scores run two tiles ahead of
-// P.V: three score buffers in tensor memory), 2 tensor-memory allocation, 4-11 softmax (two threads per
+// P.V: three score buffers in tensor memory, two P buffers in shared memory; its score MMAs are compiled in
+// as straight-line code for the usual block counts, since every instruction it spends between two MMAs is
+// tensor-core idle time), 2 tensor-memory allocation, 4-11 softmax (two threads per
 // head row, 16 tokens of the tile each; a tile's partial scores are sent to the peer one tile early, so
 // the exchange hides under the previous tile's exponentials: the softmax chain, not the tensor core or
 // HBM, paces this kernel).
 // Every wait is bounded; on expiry the CTA raises its abort flag, reports where it gave up, drains,
 // frees its tensor memory and leaves (the peer's waits then run out the same way).
+#include <type_traits>
+
 #include "sm100_common.cuh"
 
 namespace xkv {
@@ -41,7 +45,7 @@ constexpr int OFF_X = OFF_P + P_BYTES;                        // partial scores 
 constexpr int X_BYTES = (T / 4) * 128 * 16;                   // [T/4][128 rows][4 floats] = 16384
 constexpr int XW_BYTES = X_BYTES / 8;                         // one softmax warp's share of an exchange buffer
 constexpr int OFF_BAR = OFF_X + 2 * X_BYTES;                  // two exchange buffers, alternating per tile
-constexpr int OFF_MISC = OFF_BAR + 20 * 8;
+constexpr int OFF_MISC = OFF_BAR + 24 * 8;
 constexpr int OFF_RED = OFF_MISC + 16;                        // [2][128] floats: per-half row maxima / sums
 constexpr int SMEM_BYTES = OFF_RED + 1024 + 1024;
 static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
@@ -49,7 +53,10 @@ static_assert(OFF_RING % 1024 == 0 && BLK % 1024 == 0 && OFF_P % 1024 == 0, "swi
 constexpr float RESCALE_THRESHOLD = 8.f;
 constexpr uint32_t S_COL0 = 256;             // tensor-memory columns: O in 0..255, three score buffers of 32 from 256
 constexpr int SBUF = 3;
-constexpr bool kSplitOddBlock = false;      // (measured: sharing the odd block between the CTAs is 9 % slower, see make_lists)
+#ifndef XKV_LP_SPLIT_ODD
+#define XKV_LP_SPLIT_ODD 0
+#endif
+constexpr bool kSplitOddBlock = XKV_LP_SPLIT_ODD != 0;   // an odd score block out is loaded by both CTAs, each scoring half of it
 
 // The 64-column blocks one CTA of the pair works on.  Blocks [0, nv) are its own value columns (in
 // alias mode they are score blocks too); blocks with score[i] set take part in S.
@@ -58,7 +65,8 @@ struct BlockList {
   int col[MAXB];        // column (elements) inside the tensor the block is loaded from
   int src[MAXB];        // 0: key latent, 1: decoupled RoPE key part, 2: value latent
   int qcol[MAXB];       // matching column of the effective query, or -1 when the block is values only
-  int k4_lo[MAXB], k4_hi[MAXB];   // which of the block's four 16-column MMA steps this CTA scores: [lo, hi)
+  int ks0;              // first score block of the list (value-only blocks come before it)
+  uint32_t steps;       // which 16-column MMA steps of the score blocks this CTA issues: bit 4 * (i - ks0) + k4
 };
 
 struct Args {
@@ -87,12 +95,6 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t ran
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// One bulk copy from this CTA's shared memory into the peer's, counting its bytes on an mbarrier of the peer.
-__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, uint32_t src_local, uint32_t bytes, uint32_t bar_cluster) {
-  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst_cluster), "r"(src_local), "r"(bytes), "r"(bar_cluster)
-               : "memory");
 }
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -171,16 +173,17 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   auto bar_empty = [&](int s) { return bar0 + 8u * (4 + s); };        // [4] P.V of the tile that used the stage has run
   auto bar_sfull = [&](int i) { return bar0 + 8u * (8 + i); };        // [3] a score buffer holds S of a tile
   auto bar_sempty = [&](int i) { return bar0 + 8u * (11 + i); };      // [3] the softmax threads have read it
-  const uint32_t bar_pfull = bar0 + 8u * 14, bar_pempty = bar0 + 8u * 15, bar_odone = bar0 + 8u * 16;
-  auto bar_xfull = [&](int i) { return bar0 + 8u * (17 + i); };       // [2] the peer's partial scores have landed in exchange buffer i
+  auto bar_pfull = [&](int i) { return bar0 + 8u * (14 + i); };       // [2] a P buffer holds the probabilities of a tile
+  auto bar_pempty = [&](int i) { return bar0 + 8u * (16 + i); };      // [2] P.V of the tile that used it has run
+  const uint32_t bar_odone = bar0 + 8u * 18;
+  auto bar_xfull = [&](int i) { return bar0 + 8u * (19 + i); };       // [2] the peer's partial scores have landed in exchange buffer i
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 4);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
     for (int i = 0; i < SBUF; ++i) { mbar_init(bar_sfull(i), 1); mbar_init(bar_sempty(i), 256); }
-    mbar_init(bar_pfull, 256);
-    mbar_init(bar_pempty, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_pfull(i), 256); mbar_init(bar_pempty(i), 1); }
     mbar_init(bar_odone, 1);
     for (int i = 0; i < 2; ++i) mbar_init(bar_xfull(i), 1);   // one local arrive.expect_tx per use + the peer's st.async bytes
     *abort_flag = 0;
@@ -246,49 +249,63 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       // operand descriptors built once; the loops only add offsets
       const uint64_t dq0 = smem_desc(base + OFF_Q, 16, 1024), dk0 = smem_desc(base + OFF_RING, 16, 1024);
       const uint64_t dp0 = smem_desc(base + OFF_P, 16, 1024), dv0 = smem_desc(base + OFF_RING, BLK, 1024);
-      auto issue_scores = [&](int i) -> bool {
+      // One thread issues every MMA, and what it spends per instruction on addresses and loop control is time the
+      // tensor core idles (a 128 x 32 x 16 MMA takes 46 cycles): the usual step sets are compiled in, fully
+      // unrolled with constant offsets; any other set runs the loop at the end.
+      const uint64_t dks = desc_advance(dk0, (uint32_t)(bl.ks0 * BLK));
+      auto issue_scores = [&](auto steps_c, int i) -> bool {
+        constexpr uint32_t STEPS = decltype(steps_c)::value;
         const int stage = i % STAGES, sb = i % SBUF;
         if (i >= SBUF && !XKV_LP_WAIT(1, true, mbar_wait(bar_sempty(sb), ((uint32_t)(i / SBUF) & 1u) ^ 1u, abort_flag))) return false;
         if (!XKV_LP_WAIT(2, true, mbar_wait(bar_full(stage), (uint32_t)(i / STAGES) & 1u, abort_flag))) return false;
         tc_fence_after();
         const uint32_t tacc = tmem_base + S_COL0 + (uint32_t)sb * (uint32_t)T;
-        int qi = 0;
-        bool first = true;
-        for (int k = 0; k < bl.n; ++k) {
-          if (bl.qcol[k] < 0) continue;
-          const uint64_t da_b = desc_advance(dq0, (uint32_t)(qi * QBLK));
-          const uint64_t db_b = desc_advance(dk0, (uint32_t)(stage * (MAXB * BLK) + k * BLK));
-          if (bl.k4_lo[k] == 0 && bl.k4_hi[k] == 4) {
+        const uint64_t db_st = desc_advance(dks, (uint32_t)(stage * (MAXB * BLK)));
+        if constexpr (STEPS != 0u) {
 #pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4)
-              tc_mma(tacc, desc_advance(da_b, k4 * 32), desc_advance(db_b, k4 * 32), idesc_s, (first && k4 == 0) ? 0u : 1u);
-            first = false;
-          } else {
-            for (int k4 = bl.k4_lo[k]; k4 < bl.k4_hi[k]; ++k4) {
-              tc_mma(tacc, desc_advance(da_b, k4 * 32), desc_advance(db_b, k4 * 32), idesc_s, first ? 0u : 1u);
-              first = false;
+          for (int j = 0; j < 4 * MAXB; ++j)
+            if ((STEPS >> j) & 1u)
+              tc_mma(tacc, desc_advance(dq0, (uint32_t)((j >> 2) * QBLK + (j & 3) * 32)),
+                     desc_advance(db_st, (uint32_t)((j >> 2) * BLK + (j & 3) * 32)), idesc_s, (STEPS & ((1u << j) - 1u)) ? 1u : 0u);
+        } else {
+          uint32_t acc = 0u;
+          for (int j = 0; j < 4 * MAXB; ++j)
+            if ((bl.steps >> j) & 1u) {
+              tc_mma(tacc, desc_advance(dq0, (uint32_t)((j >> 2) * QBLK + (j & 3) * 32)),
+                     desc_advance(db_st, (uint32_t)((j >> 2) * BLK + (j & 3) * 32)), idesc_s, acc);
+              acc = 1u;
             }
-          }
-          ++qi;
         }
         tc_commit(bar_sfull(sb));
         return true;
       };
       // the scores run two tiles ahead of P.V: S(i+2) is in the queue before P of tile i is waited for, so the
       // softmax threads find S(i+1) finished when they turn to it in the middle of tile i
-      bool ok = issue_scores(0);
-      if (ok && ntiles > 1) ok = issue_scores(1);
-      for (int i = 0; ok && i < ntiles; ++i) {
-        if (i + 2 < ntiles) ok = issue_scores(i + 2);
-        if (!ok) break;
-        if (!XKV_LP_WAIT(3, true, mbar_wait(bar_pfull, (uint32_t)i & 1u, abort_flag))) { ok = false; break; }
-        tc_fence_after();
-        const uint64_t dv_st = desc_advance(dv0, (uint32_t)((i % STAGES) * (MAXB * BLK)));
+      auto run = [&](auto steps_c) -> bool {
+        bool ok = issue_scores(steps_c, 0);
+        if (ok && ntiles > 1) ok = issue_scores(steps_c, 1);
+        for (int i = 0; ok && i < ntiles; ++i) {
+          if (i + 2 < ntiles) ok = issue_scores(steps_c, i + 2);
+          if (!ok) break;
+          if (!XKV_LP_WAIT(3, true, mbar_wait(bar_pfull(i & 1), (uint32_t)(i >> 1) & 1u, abort_flag))) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t dv_st = desc_advance(dv0, (uint32_t)((i % STAGES) * (MAXB * BLK)));
+          const uint64_t dp_i = desc_advance(dp0, (uint32_t)((i & 1) * 64));       // the two P buffers are the halves of the 128-byte rows
 #pragma unroll
-        for (int k4 = 0; k4 < T / 16; ++k4)
-          tc_mma(tmem_base, desc_advance(dp0, k4 * 32), desc_advance(dv_st, k4 * 2048), idesc_o, (i == 0 && k4 == 0) ? 0u : 1u);
-        tc_commit(bar_empty(i % STAGES));      // the tile's blocks and ...
-        tc_commit(bar_pempty);                 // ... the P buffer are free once these MMAs have run
+          for (int k4 = 0; k4 < T / 16; ++k4)
+            tc_mma(tmem_base, desc_advance(dp_i, k4 * 32), desc_advance(dv_st, k4 * 2048), idesc_o, (i == 0 && k4 == 0) ? 0u : 1u);
+          tc_commit(bar_empty(i % STAGES));      // the tile's blocks and ...
+          tc_commit(bar_pempty(i & 1));          // ... its P buffer are free once these MMAs have run
+        }
+        return ok;
+      };
+      bool ok;
+      switch (bl.steps) {
+        case 0xFFFFu: ok = run(std::integral_constant<uint32_t, 0xFFFFu>{}); break;       // four whole blocks
+        case 0xFFFFFu: ok = run(std::integral_constant<uint32_t, 0xFFFFFu>{}); break;     // five whole blocks
+        case 0x3FFFFu: ok = run(std::integral_constant<uint32_t, 0x3FFFFu>{}); break;     // four blocks and the first half of a fifth
+        case 0xCFFFFu: ok = run(std::integral_constant<uint32_t, 0xCFFFFu>{}); break;     // four blocks and the second half of a fifth
+        default: ok = run(std::integral_constant<uint32_t, 0u>{}); break;
       }
       if (ok) tc_commit(bar_odone);
       else report(a.status, XKV_ERR_TIMEOUT, 31, tile_begin, (int)rank, b);
@@ -303,15 +320,16 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     // exchange buffers: [buffer 2][softmax warp 8][group of 4 tokens][lane][4 floats]: a warp's share is 2 KB in one piece
     const uint32_t x_warp = base + OFF_X + (uint32_t)(warp - 4) * XW_BYTES;          // + buffer * X_BYTES
     const uint32_t x_local = x_warp + (uint32_t)lane * 16u;                             // + g * 512
-    const uint32_t x_warp_peer = map_to_cta(x_warp, peer);
+    const uint32_t x_local_peer = map_to_cta(x_local, peer);
     float* red_s = reinterpret_cast<float*>(sm + OFF_RED);   // [2][128]: per-half row maxima / row sums
     float m_ref = -CUDART_INF_F, l_sum = 0.f;                // l_sum: this thread's tokens only
     bool alive = true;
     // My partial scores of a tile leave tensor memory and go to the peer one tile EARLY (in the middle of
     // the previous tile's softmax), so the exchange's latency hides under that tile's exponentials.  Two
-    // exchange buffers with a barrier each.  The partial of tile t is staged in MY buffer (t + 1) & 1 (the one I
-    // have just read tile t - 1 out of: the peer cannot write tile t + 1 into it before it has this very
-    // copy) and bulk-copied, one 2 KB piece per warp, into the PEER's buffer t & 1, counting its bytes there.
+    // exchange buffers with a barrier each.  The partial of tile t goes straight from registers into the
+    // PEER's buffer t & 1 (st.async: 16 bytes per store, counted on the peer's barrier; no staging copy and
+    // no proxy fence on the sender).  That buffer is free: the peer's partial of tile t - 1 has reached me,
+    // and every peer thread sends it only after reading tile t - 2 out of the same buffer.
     float s[TH], s_next[TH];
     auto fetch_and_send = [&](int i) {
       const int sb = i % SBUF;
@@ -325,16 +343,16 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       for (int e = 0; e < 16; ++e) s_next[e] = __uint_as_float(v0[e]);
       tc_fence_before();
       mbar_arrive(bar_sempty(sb));
-      const uint32_t stage_off = (uint32_t)((i + 1) & 1) * X_BYTES, dst_off = (uint32_t)(i & 1) * X_BYTES;
+      const uint32_t dst_off = (uint32_t)(i & 1) * X_BYTES;
       if (threadIdx.x == 128) mbar_expect_tx(bar_xfull(i & 1), X_BYTES);   // my buffer i & 1: all of the peer's bytes for tile i
+      {
+        const uint32_t bar_peer = map_to_cta(bar_xfull(i & 1), peer);
 #pragma unroll
-      for (int g4 = 0; g4 < TH / 4; ++g4)
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(x_local + stage_off + g4 * 512), "f"(s_next[4 * g4]),
-                     "f"(s_next[4 * g4 + 1]), "f"(s_next[4 * g4 + 2]), "f"(s_next[4 * g4 + 3]) : "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");         // generic writes -> the bulk copy's reads
-      __syncwarp();
-      if (lane == 0)
-        bulk_copy_to_peer(x_warp_peer + dst_off, x_warp + stage_off, XW_BYTES, map_to_cta(bar_xfull(i & 1), peer));
+        for (int g4 = 0; g4 < TH / 4; ++g4)
+          asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                       ::"r"(x_local_peer + dst_off + g4 * 512), "r"(__float_as_uint(s_next[4 * g4])), "r"(__float_as_uint(s_next[4 * g4 + 1])),
+                         "r"(__float_as_uint(s_next[4 * g4 + 2])), "r"(__float_as_uint(s_next[4 * g4 + 3])), "r"(bar_peer) : "memory");
+      }
     };
     if (ntiles > 0) fetch_and_send(0);
     for (int i = 0; i < ntiles && alive; ++i) {
@@ -374,26 +392,27 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       // ---- lazily updated reference maximum: does ANY thread see a score that tops its row's reference by
       // more than the threshold (or a first finite score)?  All 256 agree through one reducing barrier.
       const bool move_hint = tmax > m_ref + RESCALE_THRESHOLD || (m_ref == -CUDART_INF_F && tmax > -CUDART_INF_F);
-      uint32_t anym, anya;
-      {
-        const uint32_t mine = (move_hint ? 1u : 0u) | (*abort_flag ? 2u : 0u);
+      // (one barrier per tile: a raised abort flag rides on the same vote and is told apart by a second, rare one)
+      auto vote = [](uint32_t mine) -> uint32_t {
+        uint32_t r;
         asm volatile(
             "{\n\t.reg .pred p, q;\n\t"
-            "setp.ne.u32 p, %2, 0;\n\t"
+            "setp.ne.u32 p, %1, 0;\n\t"
             "barrier.cta.red.or.pred q, 1, 256, p;\n\t"
-            "selp.u32 %0, 1, 0, q;\n\t"
-            "setp.ne.u32 p, %3, 0;\n\t"
-            "barrier.cta.red.or.pred q, 1, 256, p;\n\t"
-            "selp.u32 %1, 1, 0, q;\n\t}"
-            : "=r"(anym), "=r"(anya)
-            : "r"(mine & 1u), "r"(mine & 2u)
+            "selp.u32 %0, 1, 0, q;\n\t}"
+            : "=r"(r)
+            : "r"(mine)
             : "memory");
-      }
-      if (anya) { alive = false; break; }
+        return r;
+      };
+      const uint32_t anym = vote((move_hint || *abort_flag) ? 1u : 0u);
+      if (anym && vote(*abort_flag ? 1u : 0u)) { alive = false; break; }
       XKV_LP_MARK(14);
-      // the single P buffer (and, for a rescale, the output rows) are free once P.V of the previous tile has run
-      if (i > 0 && !XKV_LP_WAIT(7, threadIdx.x == 128, mbar_wait(bar_pempty, (uint32_t)(i - 1) & 1u, abort_flag))) report(a.status, XKV_ERR_TIMEOUT, 35, tile_begin + i, (int)rank, b);
+      // this tile's P buffer is free once P.V of the tile before last has run; a rescale of the output rows has to
+      // wait for the previous tile's P.V as well
+      if (i > 1 && !XKV_LP_WAIT(7, threadIdx.x == 128, mbar_wait(bar_pempty(i & 1), (uint32_t)((i >> 1) - 1) & 1u, abort_flag))) report(a.status, XKV_ERR_TIMEOUT, 35, tile_begin + i, (int)rank, b);
       if (anym) {
+        if (i > 0 && !mbar_wait(bar_pempty((i - 1) & 1), (uint32_t)((i - 1) >> 1) & 1u, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 38, tile_begin + i, (int)rank, b);
         // rare: the two threads of a row put their maxima together, every row decides for itself, and each
         // thread rescales its half of the row's output columns in tensor memory
         red_s[half * 128 + r] = tmax;
@@ -429,12 +448,11 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         uint32_t pk[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = ex2_approx(s[c8 * 8 + 2 * e] - mref), p1 = ex2_approx(s[c8 * 8 + 2 * e + 1] - mref);
-          T_ q0 = TypeTraits<T_>::from_f(p0), q1 = TypeTraits<T_>::from_f(p1);
-          l_sum += TypeTraits<T_>::to_f(q0) + TypeTraits<T_>::to_f(q1);
-          pk[e] = (uint32_t)(*reinterpret_cast<uint16_t*>(&q0)) | ((uint32_t)(*reinterpret_cast<uint16_t*>(&q1)) << 16);
+          pk[e] = TypeTraits<T_>::pack2(ex2_approx(s[c8 * 8 + 2 * e] - mref), ex2_approx(s[c8 * 8 + 2 * e + 1] - mref));
+          const float2 q = TypeTraits<T_>::unpack2(pk[e]);
+          l_sum += q.x + q.y;
         }
-        *reinterpret_cast<uint4*>(prow + (((half * (TH / 8) + c8) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(prow + ((((i & 1) * 4 + half * (TH / 8) + c8) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       // ragged batch, last tile of the row: value rows past the row's own length may hold anything (NaN
       // included, and 0 * NaN is NaN): zero them before the MMAs read the tile
@@ -451,7 +469,7 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
       XKV_LP_MARK(16);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
-      mbar_arrive(bar_pfull);
+      mbar_arrive(bar_pfull(i & 1));
       XKV_LP_MARK(17);
     }
     // ---- output: O row / l, log-sum-exp; each thread writes its half of the row's columns ---------------
@@ -541,14 +559,16 @@ bool make_lists(const xkv_decode_params& p, BlockList out[2]) {
   }
   // score blocks not covered above: all key blocks (separate value latent) or the key blocks past the
   // value columns (alias), then the decoupled RoPE blocks
+  int k4_lo[2][MAXB], k4_hi[2][MAXB];
   for (int r = 0; r < 2; ++r)
-    for (int i = 0; i < MAXB; ++i) { out[r].k4_lo[i] = 0; out[r].k4_hi[i] = 4; }
-  auto put = [&](BlockList& l, int blk, int lo, int hi) {
+    for (int i = 0; i < MAXB; ++i) { k4_lo[r][i] = 0; k4_hi[r][i] = 4; }
+  auto put = [&](int r, int blk, int lo, int hi) {
+    BlockList& l = out[r];
     if (l.n >= MAXB) return false;
     if (blk < kb) { l.col[l.n] = blk * 64; l.src[l.n] = 0; }
     else { l.col[l.n] = (blk - kb) * 64; l.src[l.n] = 1; }
     l.qcol[l.n] = blk * 64;
-    l.k4_lo[l.n] = lo; l.k4_hi[l.n] = hi;
+    k4_lo[r][l.n] = lo; k4_hi[r][l.n] = hi;
     ++l.n;
     return true;
   };
@@ -557,16 +577,27 @@ bool make_lists(const xkv_decode_params& p, BlockList out[2]) {
     // an odd block out (MLA: the decoupled RoPE block) is loaded by both CTAs and each scores half of its
     // MMA steps, so both issue the same number of score MMAs per tile
     if (kSplitOddBlock && blk == kb + tb - 1 && (extras & 1) && out[0].n == out[1].n) {
-      if (!put(out[0], blk, 0, 2) || !put(out[1], blk, 2, 4)) return false;
-    } else if (!put(out[out[0].n <= out[1].n ? 0 : 1], blk, 0, 4)) {
+      if (!put(0, blk, 0, 2) || !put(1, blk, 2, 4)) return false;
+    } else if (!put(out[0].n <= out[1].n ? 0 : 1, blk, 0, 4)) {
       return false;
     }
   }
   // each CTA must score at least one block (its score buffer is exchanged every tile)
   for (int r = 0; r < 2; ++r) {
+    BlockList& l = out[r];
     int ns = 0;
-    for (int i = 0; i < out[r].n; ++i) ns += out[r].qcol[i] >= 0;
-    if (ns == 0 || out[r].n > MAXB) return false;
+    l.ks0 = -1;
+    l.steps = 0u;
+    for (int i = 0; i < l.n; ++i) {
+      if (l.qcol[i] < 0) {
+        if (l.ks0 >= 0) return false;               // value-only blocks come first
+        continue;
+      }
+      if (l.ks0 < 0) l.ks0 = i;
+      for (int k4 = k4_lo[r][i]; k4 < k4_hi[r][i]; ++k4) l.steps |= 1u << (4 * (i - l.ks0) + k4);
+      ++ns;
+    }
+    if (ns == 0 || l.n > MAXB) return false;
   }
   return true;
 }

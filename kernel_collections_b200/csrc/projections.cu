@@ -6,7 +6,7 @@
 // 64 with 128 heads that is 1 GB of L2 traffic per call on each side, more than the cache the attention
 // itself streams.  Here one CTA owns a 128-column strip of one head's matrix and walks the batch in
 // chunks, so the matrix is read once per chunk of 16 rows (grid: strips x heads x batch chunks).
-#include "xkv_internal.h"
+#include "sm100_common.cuh"
 
 namespace xkv {
 namespace {
@@ -72,6 +72,128 @@ batched_projection_kernel(const TI* __restrict__ x, int64_t x_sb, int64_t x_sh, 
     if (j < nb) out[(int64_t)(b0 + j) * o_sb + (int64_t)h * o_sh + c] = from_f<TO>(acc[j]);
 }
 
+// ---- the same product on the tensor cores (mma.sync m16n8k16, fp32 accumulation) -------------------------------
+// One CTA of four warps owns, for one head, a tile of MM = 64 batch rows x MN = 64 output columns and walks the
+// contraction in chunks of MK = 64: the chunk of x and of the head's matrix are staged in shared memory as 16-bit
+// values, warp w multiplies rows 16 w .. 16 w + 15.  fp32 inputs (merged latent rows) are split into a rounded
+// 16-bit value and the 16-bit remainder and multiplied twice, so the product keeps the input's precision.
+// W_K says which index of the matrix is contiguous in memory: the contraction index (w_si == 1) or the output column
+// (w_sc == 1).  Rows of a strip past `batch` are zero.  `tail`: the absorbed query's pass-through columns, copied
+// by the CTAs of strip 0.
+constexpr int MM = 64, MN = 64, MK = 64, MPAD = 8;
+
+template <typename TI, typename T, bool W_K>
+__global__ void __launch_bounds__(128)
+projection_mma_kernel(const TI* __restrict__ x, int64_t x_sb, int64_t x_sh, const T* __restrict__ w, int div, int64_t w_sh,
+                      int64_t w_si, int64_t w_sc, T* __restrict__ out, int64_t o_sb, int64_t o_sh, int batch, int in_dim,
+                      int out_dim, const T* __restrict__ tail, int64_t t_sb, int64_t t_sh, int tail_dim, int tail_col) {
+  constexpr bool SPLIT = sizeof(TI) == 4;
+  __shared__ __align__(16) T xs[SPLIT ? 2 : 1][MM][MK + MPAD];
+  __shared__ __align__(16) T ws[MK][MN + MPAD];            // W_K: [column][contraction], else [contraction][column]
+  const int h = blockIdx.y, c0 = blockIdx.x * MN, b0 = blockIdx.z * MM;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const T* wh = w + (int64_t)(h / div) * w_sh;
+  if (tail != nullptr && blockIdx.x == 0) {
+    for (int idx = threadIdx.x; idx < MM * tail_dim; idx += 128) {
+      const int j = idx / tail_dim, d = idx - j * tail_dim;
+      if (b0 + j < batch) out[(int64_t)(b0 + j) * o_sb + (int64_t)h * o_sh + tail_col + d] = tail[(int64_t)(b0 + j) * t_sb + (int64_t)h * t_sh + d];
+    }
+  }
+  float acc[MN / 8][4];
+#pragma unroll
+  for (int n = 0; n < MN / 8; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+
+  for (int k0 = 0; k0 < in_dim; k0 += MK) {
+    __syncthreads();
+    // x chunk: 64 rows x 64 values, 8 values per thread and pass
+    for (int idx = threadIdx.x; idx < MM * (MK / 8); idx += 128) {
+      const int j = idx / (MK / 8), k8 = (idx - j * (MK / 8)) * 8;
+      const TI* src = x + (int64_t)(b0 + j) * x_sb + (int64_t)h * x_sh + k0 + k8;
+      if constexpr (SPLIT) {
+        T hi[8], lo[8];
+        if (b0 + j < batch) {
+          const float4 f0 = *reinterpret_cast<const float4*>(src), f1 = *reinterpret_cast<const float4*>(src + 4);
+          const float f[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            hi[e] = sm100::TypeTraits<T>::from_f(f[e]);
+            lo[e] = sm100::TypeTraits<T>::from_f(f[e] - sm100::TypeTraits<T>::to_f(hi[e]));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { hi[e] = sm100::TypeTraits<T>::from_f(0.f); lo[e] = hi[e]; }
+        }
+        *reinterpret_cast<uint4*>(&xs[0][j][k8]) = *reinterpret_cast<const uint4*>(hi);
+        *reinterpret_cast<uint4*>(&xs[SPLIT ? 1 : 0][j][k8]) = *reinterpret_cast<const uint4*>(lo);
+      } else {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (b0 + j < batch) v = *reinterpret_cast<const uint4*>(src);
+        *reinterpret_cast<uint4*>(&xs[0][j][k8]) = v;
+      }
+    }
+    // matrix chunk: 64 x 64 values in 16-byte pieces along the contiguous index
+    for (int idx = threadIdx.x; idx < MK * (MN / 8); idx += 128) {
+      const int r = idx / 8, q8 = (idx & 7) * 8;
+      const T* src = W_K ? wh + (int64_t)(c0 + r) * w_sc + (k0 + q8) : wh + (int64_t)(k0 + r) * w_si + (c0 + q8);
+      *reinterpret_cast<uint4*>(&ws[r][q8]) = *reinterpret_cast<const uint4*>(src);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MK; kk += 16) {
+      uint32_t a[SPLIT ? 2 : 1][4];
+#pragma unroll
+      for (int part = 0; part < (SPLIT ? 2 : 1); ++part) {
+        a[part][0] = *reinterpret_cast<const uint32_t*>(&xs[part][warp * 16 + g][kk + 2 * t]);
+        a[part][1] = *reinterpret_cast<const uint32_t*>(&xs[part][warp * 16 + g + 8][kk + 2 * t]);
+        a[part][2] = *reinterpret_cast<const uint32_t*>(&xs[part][warp * 16 + g][kk + 2 * t + 8]);
+        a[part][3] = *reinterpret_cast<const uint32_t*>(&xs[part][warp * 16 + g + 8][kk + 2 * t + 8]);
+      }
+#pragma unroll
+      for (int n = 0; n < MN / 8; ++n) {
+        uint32_t b0r, b1r;
+        if constexpr (W_K) {
+          b0r = *reinterpret_cast<const uint32_t*>(&ws[n * 8 + g][kk + 2 * t]);
+          b1r = *reinterpret_cast<const uint32_t*>(&ws[n * 8 + g][kk + 2 * t + 8]);
+        } else {
+          // rows of ws are contraction indices: the transposing matrix load hands every thread its (k, k + 1) pairs
+          const uint32_t addr = sm100::smem_u32(&ws[kk + (lane & 15)][n * 8]);
+          asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(b0r), "=r"(b1r) : "r"(addr));
+        }
+#pragma unroll
+        for (int part = 0; part < (SPLIT ? 2 : 1); ++part) sm100::TypeTraits<T>::mma(acc[n], a[part], b0r, b1r);
+      }
+    }
+  }
+  const int r0 = b0 + warp * 16 + g;
+#pragma unroll
+  for (int n = 0; n < MN / 8; ++n) {
+    const int c = c0 + n * 8 + 2 * t;
+    if (c >= out_dim) continue;
+    T* o0 = out + (int64_t)r0 * o_sb + (int64_t)h * o_sh + c;
+    T* o1 = out + (int64_t)(r0 + 8) * o_sb + (int64_t)h * o_sh + c;
+    const T v00 = sm100::TypeTraits<T>::from_f(acc[n][0]), v01 = sm100::TypeTraits<T>::from_f(acc[n][1]);
+    const T v10 = sm100::TypeTraits<T>::from_f(acc[n][2]), v11 = sm100::TypeTraits<T>::from_f(acc[n][3]);
+    if (r0 < batch) { o0[0] = v00; o0[1] = v01; }
+    if (r0 + 8 < batch) { o1[0] = v10; o1[1] = v11; }
+  }
+}
+
+// Whether the tensor-core kernel can take a product: whole 64-wide chunks, one contiguous matrix index, 16-byte
+// aligned rows everywhere it loads 16 bytes at a time.
+template <typename TI>
+bool projection_mma_ok(const void* x, int64_t x_sb, int64_t x_sh, const void* w, int64_t w_sh, int64_t w_si, int64_t w_sc,
+                       int in_dim, int out_dim) {
+  const int xa = 16 / (int)sizeof(TI);
+  if (in_dim % MK != 0 || out_dim % MN != 0) return false;
+  if (!sm100::aligned16(x) || x_sb % xa != 0 || x_sh % xa != 0) return false;
+  if (!sm100::aligned16(w) || w_sh % 8 != 0) return false;
+  if (w_si == 1) return w_sc % 8 == 0;
+  if (w_sc == 1) return w_si % 8 == 0;
+  return false;
+}
+
 template <typename T>
 __global__ void copy_tail_kernel(const T* __restrict__ qt, int64_t qt_sb, int64_t qt_sh, T* __restrict__ out, int dk,
                                  int k_rank, int tail, int num_heads) {
@@ -91,8 +213,22 @@ bool batched_projection_fits(int batch, int in_dim) {
 template <typename T>
 static int absorb_batched(const xkv_decode_params& p, T* qeff, int dk, cudaStream_t st) {
   const int div = p.num_heads / p.k_proj_heads;
-  const dim3 grid((unsigned)ceil_div(p.k_rank, NT), (unsigned)p.num_heads, (unsigned)ceil_div(p.batch, BC));
   // w[h/div, i = d, c = r] = k_proj[(h/div) * kp_sh + r * kp_sr + d * kp_sd]
+  if (projection_mma_ok<T>(p.q, p.q_sb, p.q_sh, p.k_proj, p.kp_sh, p.kp_sd, p.kp_sr, p.head_dim, p.k_rank) && dk % 2 == 0 &&
+      (p.tail_dim == 0 || p.q_tail != nullptr)) {
+    const dim3 mgrid((unsigned)(p.k_rank / MN), (unsigned)p.num_heads, (unsigned)ceil_div(p.batch, MM));
+    const T* tail = p.tail_dim > 0 ? static_cast<const T*>(p.q_tail) : nullptr;
+    if (p.kp_sd == 1)
+      projection_mma_kernel<T, T, true><<<mgrid, 128, 0, st>>>(static_cast<const T*>(p.q), p.q_sb, p.q_sh,
+          static_cast<const T*>(p.k_proj), div, p.kp_sh, p.kp_sd, p.kp_sr, qeff, (int64_t)p.num_heads * dk, (int64_t)dk, p.batch,
+          p.head_dim, p.k_rank, tail, p.qt_sb, p.qt_sh, p.tail_dim, p.k_rank);
+    else
+      projection_mma_kernel<T, T, false><<<mgrid, 128, 0, st>>>(static_cast<const T*>(p.q), p.q_sb, p.q_sh,
+          static_cast<const T*>(p.k_proj), div, p.kp_sh, p.kp_sd, p.kp_sr, qeff, (int64_t)p.num_heads * dk, (int64_t)dk, p.batch,
+          p.head_dim, p.k_rank, tail, p.qt_sb, p.qt_sh, p.tail_dim, p.k_rank);
+    return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
+  }
+  const dim3 grid((unsigned)ceil_div(p.k_rank, NT), (unsigned)p.num_heads, (unsigned)ceil_div(p.batch, BC));
   batched_projection_kernel<T, T, T><<<grid, NT, (size_t)BC * p.head_dim * sizeof(float), st>>>(
       static_cast<const T*>(p.q), p.q_sb, p.q_sh, static_cast<const T*>(p.k_proj), div, p.kp_sh, p.kp_sd, p.kp_sr, qeff,
       (int64_t)p.num_heads * dk, (int64_t)dk, p.batch, p.head_dim, p.k_rank);
@@ -114,6 +250,18 @@ int launch_value_projection_batched(const float* o_lat, const xkv_decode_params&
   const dim3 grid((unsigned)ceil_div(p.value_dim, NT), (unsigned)p.num_heads, (unsigned)ceil_div(p.batch, BC));
   const size_t smem = (size_t)BC * p.v_rank * sizeof(float);
   const int64_t l_sb = (int64_t)p.num_heads * p.v_rank, l_sh = p.v_rank;
+  // w[h/div, i = r, c = d] = v_proj[(h/div) * vp_sh + r * vp_sr + d * vp_sd]
+  if ((p.dtype == XKV_BF16 || p.dtype == XKV_F16) && p.o_sb % 2 == 0 && p.o_sh % 2 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 3u) == 0 &&
+      projection_mma_ok<float>(o_lat, l_sb, l_sh, p.v_proj, p.vp_sh, p.vp_sr, p.vp_sd, p.v_rank, p.value_dim)) {
+    const dim3 mgrid((unsigned)(p.value_dim / MN), (unsigned)p.num_heads, (unsigned)ceil_div(p.batch, MM));
+#define XKV_VPM(T, WK)                                                                                                   \
+  projection_mma_kernel<float, T, WK><<<mgrid, 128, 0, st>>>(o_lat, l_sb, l_sh, static_cast<const T*>(p.v_proj), div, p.vp_sh, \
+      p.vp_sr, p.vp_sd, static_cast<T*>(p.out), p.o_sb, p.o_sh, p.batch, p.v_rank, p.value_dim, nullptr, 0, 0, 0, 0)
+    if (p.dtype == XKV_BF16) { if (p.vp_sr == 1) XKV_VPM(__nv_bfloat16, true); else XKV_VPM(__nv_bfloat16, false); }
+    else { if (p.vp_sr == 1) XKV_VPM(__half, true); else XKV_VPM(__half, false); }
+#undef XKV_VPM
+    return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
+  }
 #define XKV_VP(T)                                                                                                     \
   batched_projection_kernel<float, T, T><<<grid, NT, smem, st>>>(o_lat, l_sb, l_sh, static_cast<const T*>(p.v_proj), div, \
                                                                   p.vp_sh, p.vp_sr, p.vp_sd, static_cast<T*>(p.out), p.o_sb, \

@@ -86,6 +86,15 @@ template <> struct TypeTraits<__nv_bfloat16> {
   static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
   static __device__ __forceinline__ uint32_t ones2() { return 0x3F803F80u; }
+  // two floats rounded and packed by one instruction (lo in bits 0-15), and the rounded values back as floats
+  static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
+  static __device__ __forceinline__ float2 unpack2(uint32_t v) {
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+  }
   static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -98,6 +107,14 @@ template <> struct TypeTraits<__half> {
   static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
   static __device__ __forceinline__ uint32_t ones2() { return 0x3C003C00u; }
+  static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
+  static __device__ __forceinline__ float2 unpack2(uint32_t v) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
+  }
   static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"

@@ -91,6 +91,45 @@ def test_mla(dtype, case):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("k_major", [False, True])
+@pytest.mark.parametrize("case", [(5, 64, 256, 64, 300), (70, 128, 512, 64, 130), (16, 72, 128, 0, 90)])
+def test_mla_absorbed_with_batch_wide_projections(dtype, k_major, case):
+    """W_uk folded into the queries and W_uv applied to the merged latent rows as tensor-core products over the
+    whole batch (projection matrices shared by the batch, 4 rows or more): batches that do not fill a 64-row
+    strip and ones that need two, head counts off the block size, and both memory orders of the matrices
+    (contraction index contiguous or output column contiguous), against the oracle."""
+    b, H, lora, rope, L = case
+    g = torch.Generator().manual_seed(46)
+    nope, vd = 128, 128
+    qq = torch.randn(b, H, nope, generator=g).to(dtype)
+    qr = (torch.randn(b, H, rope, generator=g) / 3).to(dtype) if rope else None
+    c = (torch.randn(b, L, lora, generator=g) / 3).to(dtype)
+    kr = (torch.randn(b, L, rope, generator=g) / 3).to(dtype) if rope else None
+    Wk = (torch.randn(H, nope, lora, generator=g) / lora ** 0.5).to(dtype)
+    Wv = (torch.randn(H, lora, vd, generator=g) / lora ** 0.5).to(dtype)
+    sc = (nope + rope) ** -0.5
+    dev = lambda x: None if x is None else x.to(DEV)
+    # k_proj is indexed (batch, head, rank, head_dim), v_proj (batch, head, rank, value_dim)
+    if k_major:     # the contraction index is the contiguous one: head_dim for W_uk, rank for W_uv
+        kp = Wk.permute(0, 2, 1).contiguous().to(DEV).unsqueeze(0)
+        vp = Wv.permute(0, 2, 1).contiguous().to(DEV).permute(0, 2, 1).unsqueeze(0)
+    else:           # the output column is the contiguous one
+        kp = Wk.to(DEV).permute(0, 2, 1).unsqueeze(0)
+        vp = Wv.to(DEV).unsqueeze(0)
+    cd = dev(c)
+    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT, q=dev(qq), k=cd, v=cd, k_proj=kp, v_proj=vp,
+              q_tail=dev(qr), k_tail=dev(kr), sm_scale=sc, num_kv_heads=1)
+    assert ops.plan(**kw) == "latent_pair"
+    got = ops.decode(entry="xkv_mla_decode", **kw)
+    status_ok()
+    zr = torch.zeros(b, H, 0, dtype=dtype)
+    zk = torch.zeros(b, L, 0, dtype=dtype)
+    want = O.mla_absorbed(qq, qr if rope else zr, c, kr if rope else zk, Wk, Wv, sc)
+    close(got, want, "latent_pair with batch-wide projections")
+    assert torch.equal(got, ops.decode(entry="xkv_mla_decode", **kw))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("case", [(2, 32, 576, 512, 1100), (1, 16, 320, 256, 70), (1, 128, 576, 512, 333)])
 def test_packed_single_kv_head_cache(dtype, case):
     """The packed MLA layout of flash_decoding.mla (keys = [latent | rope], values = a prefix of the
