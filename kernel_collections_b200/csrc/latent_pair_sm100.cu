@@ -22,6 +22,7 @@
 // HBM, paces this kernel).
 // Every wait is bounded; on expiry the CTA raises its abort flag, reports where it gave up, drains,
 // frees its tensor memory and leaves (the peer's waits then run out the same way).
+#include <algorithm>
 #include <type_traits>
 
 #include "sm100_common.cuh"
@@ -151,12 +152,15 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmKt,
                    const __grid_constant__ CUtensorMap tmV, const Args a) {
   extern __shared__ uint8_t smem_raw[];
+#ifdef XKV_TC_PROFILE
+  const long long t_entry_ = clock64();
+#endif
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank(), peer = rank ^ 1u;
-  const int split = blockIdx.x >> 1, hb = blockIdx.y, b = blockIdx.z;
+  const int hb = blockIdx.x >> 1, b = blockIdx.y, split = blockIdx.z;
   const BlockList& bl = a.bl[rank];
   const int h0 = hb * 128;
   const int row_len = a.kv_lens ? min(max(a.kv_lens[b], 0), a.kv_len) : a.kv_len;
@@ -197,16 +201,28 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   // resident queries: the score blocks of this CTA, rows past num_heads are zero
   {
     const T_* qg = static_cast<const T_*>(a.qeff) + ((int64_t)b * a.num_heads + h0) * a.dk;
-    int qi = 0;
-    for (int i = 0; i < bl.n; ++i) {
-      if (bl.qcol[i] < 0) continue;
-      for (int c = threadIdx.x; c < 128 * 8; c += NTHREADS) {
-        const int r = c >> 3, ch = c & 7;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (h0 + r < a.num_heads) v = *reinterpret_cast<const uint4*>(qg + (int64_t)r * a.dk + bl.qcol[i] + ch * 8);
-        *reinterpret_cast<uint4*>(sm + OFF_Q + qi * QBLK + r * 128 + ((ch ^ (r & 7)) << 4)) = v;
+    // the score blocks are the last ones of the list, query block qi belongs to list entry ks0 + qi; four
+    // 16-byte loads are in flight per thread before the first one is stored
+    const int nq = (bl.n - bl.ks0) * 1024;
+    for (int i0 = threadIdx.x; i0 < nq; i0 += 4 * NTHREADS) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = i0 + u * NTHREADS;
+        v[u] = make_uint4(0, 0, 0, 0);
+        if (idx < nq) {
+          const int qi = idx >> 10, r = (idx >> 3) & 127, ch = idx & 7;
+          if (h0 + r < a.num_heads) v[u] = *reinterpret_cast<const uint4*>(qg + (int64_t)r * a.dk + bl.qcol[bl.ks0 + qi] + ch * 8);
+        }
       }
-      ++qi;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = i0 + u * NTHREADS;
+        if (idx < nq) {
+          const int qi = idx >> 10, r = (idx >> 3) & 127, ch = idx & 7;
+          *reinterpret_cast<uint4*>(sm + OFF_Q + qi * QBLK + r * 128 + ((ch ^ (r & 7)) << 4)) = v[u];
+        }
+      }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
   }
@@ -218,6 +234,8 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 #ifdef XKV_TC_PROFILE
   const long long t_start_ = clock64();
   const uint64_t ns_start_ = global_ns();
+  long long t_loop_end_ = t_start_, t_odone_ = t_start_;
+  if (threadIdx.x == 128) atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 18, (unsigned long long)(t_start_ - t_entry_));
 #endif
 
   if (warp == 0) {
@@ -473,10 +491,16 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       XKV_LP_MARK(17);
     }
     // ---- output: O row / l, log-sum-exp; each thread writes its half of the row's columns ---------------
+#ifdef XKV_TC_PROFILE
+    t_loop_end_ = clock64();
+#endif
     if (alive && ntiles > 0) {
       if (!mbar_wait(bar_odone, 0, abort_flag)) report(a.status, XKV_ERR_TIMEOUT, 37, tile_end, (int)rank, b);
       tc_fence_after();
     }
+#ifdef XKV_TC_PROFILE
+    t_odone_ = clock64();
+#endif
     red_s[half * 128 + r] = l_sum;
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (alive && !*abort_flag) {
@@ -510,8 +534,12 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 #ifdef XKV_TC_PROFILE
   if (threadIdx.x == 128)
     atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 8, (unsigned long long)(clock64() - t_start_));
-  if (threadIdx.x == 128)
+  if (threadIdx.x == 128) {
     atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 9, (unsigned long long)(global_ns() - ns_start_));
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 19, (unsigned long long)(t_loop_end_ - t_start_));
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 20, (unsigned long long)(t_odone_ - t_loop_end_));
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.status + 8) + 21, (unsigned long long)(clock64() - t_odone_));
+  }
 #endif
   __syncwarp();
   tc_fence_before();
@@ -611,7 +639,7 @@ int launch(const CUtensorMap& tK, const CUtensorMap& tKt, const CUtensorMap& tV,
     return XKV_ERR_LAUNCH;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(a.num_splits * 2, head_blocks, a.batch);
+  cfg.gridDim = dim3(head_blocks * 2, a.batch, a.num_splits);
   cfg.blockDim = dim3(NTHREADS);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cfg.stream = st;
@@ -629,6 +657,41 @@ int launch(const CUtensorMap& tK, const CUtensorMap& tKt, const CUtensorMap& tV,
   return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
 }
 
+// How many CTA pairs of this kernel the device holds at once.  Not simply SMs / 2: the two CTAs of a cluster
+// must sit in one GPC, and a GPC with an odd number of usable SMs leaves one over.  Asked of the runtime once
+// per device; without a device (planning on a CPU-only machine) SMs / 2.
+int pair_slots() {
+  constexpr int kMaxDevices = 64;
+  static int cached[kMaxDevices] = {};
+  const int fallback = device_sm_count() / 2;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return fallback;
+  }
+  if (dev >= 0 && dev < kMaxDevices && cached[dev] > 0) return cached[dev];
+  auto kern = latent_pair_kernel<__nv_bfloat16>;
+  int n = 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * device_sm_count(), 1, 1);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+      cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return fallback;
+  }
+  if (dev >= 0 && dev < kMaxDevices) cached[dev] = n;
+  return n;
+}
+
 }  // namespace
 
 bool latent_pair_supported(const xkv_decode_params& p) {
@@ -637,6 +700,7 @@ bool latent_pair_supported(const xkv_decode_params& p) {
   if (p.dtype != XKV_BF16 && p.dtype != XKV_F16) return false;
   if (p.logit_cap > 0.f || p.mask) return false;
   if (p.num_heads < 64) return false;      // fewer heads leave most MMA rows empty: the mma.sync kernel serves them
+  if (p.batch > 65535) return false;       // the batch row is a grid y index
   if (p.k_rank % 64 != 0 || p.tail_dim % 64 != 0 || p.v_rank % 128 != 0 || p.v_rank > 512) return false;
   if (!aligned16(p.k) || !aligned16(p.v) || !stride_ok(p.k_sl) || !stride_ok(p.v_sl)) return false;
   if (p.batch > 1 && (!stride_ok(p.k_sb) || !stride_ok(p.v_sb))) return false;
@@ -649,7 +713,7 @@ bool latent_pair_plan(const xkv_decode_params& p, LatentTcPlan* pl) {
   const int head_blocks = ceil_div(p.num_heads, 128);
   const int tiles = ceil_div(p.kv_len, T);
   const int rows = p.batch * head_blocks;
-  const int slots = device_sm_count() / 2;      // clusters of two CTAs
+  const int slots = pair_slots();               // clusters of two CTAs the device holds at once
   int best_s = 1;
   int64_t best_cost = -1;
   const int max_s = tiles < 64 ? tiles : 64;
@@ -721,6 +785,8 @@ int latent_pair_decode(const xkv_decode_params& p, const LatentTcPlan& pl, void*
   if (rc != XKV_OK) return rc;
   if (pl.off_olat != 0 && pl.num_splits == 1 && !p.lse_out)   // one split: its normalised partial IS the latent output
     return launch_value_projection_batched(a.partial_o, p, st);
+  if (pl.off_olat != 0 && !p.lse_out && value_projection_merges(p, pl.num_splits))   // a few splits: merged as the projection stages them
+    return launch_value_projection_batched(a.partial_o, p, st, a.lse, pl.num_splits);
   if (pl.off_olat != 0) {
     // merge the splits in latent space (fp32), then apply the shared value projection batched over the rows
     float* o_lat = reinterpret_cast<float*>(w + pl.off_olat);

@@ -81,22 +81,29 @@ batched_projection_kernel(const TI* __restrict__ x, int64_t x_sb, int64_t x_sh, 
 // (w_sc == 1).  Rows of a strip past `batch` are zero.  `tail`: the absorbed query's pass-through columns, copied
 // by the CTAs of strip 0.
 constexpr int MM = 64, MN = 64, MK = 64, MPAD = 8;
+constexpr int MERGE_MAX = 16;     // most splits the fp32 staging merges on the way
 
 template <typename TI, typename T, bool W_K>
 __global__ void __launch_bounds__(128)
 projection_mma_kernel(const TI* __restrict__ x, int64_t x_sb, int64_t x_sh, const T* __restrict__ w, int div, int64_t w_sh,
                       int64_t w_si, int64_t w_sc, T* __restrict__ out, int64_t o_sb, int64_t o_sh, int batch, int in_dim,
-                      int out_dim, const T* __restrict__ tail, int64_t t_sb, int64_t t_sh, int tail_dim, int tail_col) {
+                      int out_dim, const T* __restrict__ tail, int64_t t_sb, int64_t t_sh, int tail_dim, int tail_col,
+                      const float* __restrict__ lse, int nsplit) {
   constexpr bool SPLIT = sizeof(TI) == 4;
+  __shared__ float wsp[SPLIT ? MM : 1][SPLIT ? MERGE_MAX : 1];   // merge weights of the strip's rows
   __shared__ __align__(16) T xs[SPLIT ? 2 : 1][MM][MK + MPAD];
   __shared__ __align__(16) T ws[MK][MN + MPAD];            // W_K: [column][contraction], else [contraction][column]
   const int h = blockIdx.y, c0 = blockIdx.x * MN, b0 = blockIdx.z * MM;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const T* wh = w + (int64_t)(h / div) * w_sh;
   if (tail != nullptr && blockIdx.x == 0) {
-    for (int idx = threadIdx.x; idx < MM * tail_dim; idx += 128) {
-      const int j = idx / tail_dim, d = idx - j * tail_dim;
-      if (b0 + j < batch) out[(int64_t)(b0 + j) * o_sb + (int64_t)h * o_sh + tail_col + d] = tail[(int64_t)(b0 + j) * t_sb + (int64_t)h * t_sh + d];
+    // (the launcher has checked: tail_dim a multiple of 8, 16-byte aligned rows on both sides)
+    const int per_row = tail_dim / 8;
+    for (int idx = threadIdx.x; idx < MM * per_row; idx += 128) {
+      const int j = idx / per_row, d = (idx - j * per_row) * 8;
+      if (b0 + j < batch)
+        *reinterpret_cast<uint4*>(out + (int64_t)(b0 + j) * o_sb + (int64_t)h * o_sh + tail_col + d) =
+            *reinterpret_cast<const uint4*>(tail + (int64_t)(b0 + j) * t_sb + (int64_t)h * t_sh + d);
     }
   }
   float acc[MN / 8][4];
@@ -104,42 +111,104 @@ projection_mma_kernel(const TI* __restrict__ x, int64_t x_sb, int64_t x_sh, cons
   for (int n = 0; n < MN / 8; ++n)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+  if constexpr (SPLIT) {
+    // x given as per-split partial rows (each normalised) and their log-sum-exps: the merged row is their
+    // combination with weights exp(lse_s - max) / sum; an empty split has lse = -inf and weight 0
+    if (nsplit > 1 && threadIdx.x < MM) {
+      const int j = threadIdx.x;
+      float l[MERGE_MAX], mx = -CUDART_INF_F, sum = 0.f;
+      for (int sidx = 0; sidx < nsplit; ++sidx) {
+        l[sidx] = b0 + j < batch ? lse[((int64_t)(b0 + j) * gridDim.y + h) * nsplit + sidx] : -CUDART_INF_F;
+        mx = fmaxf(mx, l[sidx]);
+      }
+      for (int sidx = 0; sidx < nsplit; ++sidx) {
+        l[sidx] = mx == -CUDART_INF_F ? 0.f : __expf(l[sidx] - mx);
+        sum += l[sidx];
+      }
+      for (int sidx = 0; sidx < nsplit; ++sidx) wsp[j][sidx] = sum > 0.f ? l[sidx] / sum : 0.f;
+    }
+  }
 
-  for (int k0 = 0; k0 < in_dim; k0 += MK) {
-    __syncthreads();
-    // x chunk: 64 rows x 64 values, 8 values per thread and pass
-    for (int idx = threadIdx.x; idx < MM * (MK / 8); idx += 128) {
+  // Software pipeline: the next chunk's global loads are issued into registers before the current chunk's MMAs,
+  // so a chunk costs the longer of the two, not their sum (the CTAs are too few to hide the latency by themselves).
+  constexpr int XI = MM * (MK / 8) / 128;      // 16-byte (8-value) pieces of x per thread and chunk
+  constexpr int WI = MK * (MN / 8) / 128;      // 16-byte pieces of the matrix per thread and chunk
+  float4 xr[SPLIT ? XI : 1][2];
+  uint4 xr16[SPLIT ? 1 : XI];
+  uint4 wr[WI];
+  (void)xr; (void)xr16;
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int it = 0; it < XI; ++it) {
+      const int idx = threadIdx.x + it * 128;
       const int j = idx / (MK / 8), k8 = (idx - j * (MK / 8)) * 8;
       const TI* src = x + (int64_t)(b0 + j) * x_sb + (int64_t)h * x_sh + k0 + k8;
       if constexpr (SPLIT) {
-        T hi[8], lo[8];
+        float4 f0 = make_float4(0.f, 0.f, 0.f, 0.f), f1 = f0;
         if (b0 + j < batch) {
-          const float4 f0 = *reinterpret_cast<const float4*>(src), f1 = *reinterpret_cast<const float4*>(src + 4);
-          const float f[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            hi[e] = sm100::TypeTraits<T>::from_f(f[e]);
-            lo[e] = sm100::TypeTraits<T>::from_f(f[e] - sm100::TypeTraits<T>::to_f(hi[e]));
+          f0 = *reinterpret_cast<const float4*>(src);
+          f1 = *reinterpret_cast<const float4*>(src + 4);
+          if (nsplit > 1) {
+            const float w0 = wsp[j][0];
+            f0 = make_float4(f0.x * w0, f0.y * w0, f0.z * w0, f0.w * w0);
+            f1 = make_float4(f1.x * w0, f1.y * w0, f1.z * w0, f1.w * w0);
+            for (int sidx = 1; sidx < nsplit; ++sidx) {
+              const float wv = wsp[j][sidx];
+              const float4 g0 = *reinterpret_cast<const float4*>(src + (int64_t)sidx * in_dim);
+              const float4 g1 = *reinterpret_cast<const float4*>(src + (int64_t)sidx * in_dim + 4);
+              f0 = make_float4(fmaf(g0.x, wv, f0.x), fmaf(g0.y, wv, f0.y), fmaf(g0.z, wv, f0.z), fmaf(g0.w, wv, f0.w));
+              f1 = make_float4(fmaf(g1.x, wv, f1.x), fmaf(g1.y, wv, f1.y), fmaf(g1.z, wv, f1.z), fmaf(g1.w, wv, f1.w));
+            }
           }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) { hi[e] = sm100::TypeTraits<T>::from_f(0.f); lo[e] = hi[e]; }
         }
-        *reinterpret_cast<uint4*>(&xs[0][j][k8]) = *reinterpret_cast<const uint4*>(hi);
-        *reinterpret_cast<uint4*>(&xs[SPLIT ? 1 : 0][j][k8]) = *reinterpret_cast<const uint4*>(lo);
+        xr[it][0] = f0;
+        xr[it][1] = f1;
       } else {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (b0 + j < batch) v = *reinterpret_cast<const uint4*>(src);
-        *reinterpret_cast<uint4*>(&xs[0][j][k8]) = v;
+        xr16[it] = b0 + j < batch ? *reinterpret_cast<const uint4*>(src) : make_uint4(0u, 0u, 0u, 0u);
       }
     }
-    // matrix chunk: 64 x 64 values in 16-byte pieces along the contiguous index
-    for (int idx = threadIdx.x; idx < MK * (MN / 8); idx += 128) {
+#pragma unroll
+    for (int it = 0; it < WI; ++it) {
+      const int idx = threadIdx.x + it * 128;
       const int r = idx / 8, q8 = (idx & 7) * 8;
       const T* src = W_K ? wh + (int64_t)(c0 + r) * w_sc + (k0 + q8) : wh + (int64_t)(k0 + r) * w_si + (c0 + q8);
-      *reinterpret_cast<uint4*>(&ws[r][q8]) = *reinterpret_cast<const uint4*>(src);
+      wr[it] = *reinterpret_cast<const uint4*>(src);
     }
+  };
+  auto stage = [&]() {
+#pragma unroll
+    for (int it = 0; it < XI; ++it) {
+      const int idx = threadIdx.x + it * 128;
+      const int j = idx / (MK / 8), k8 = (idx - j * (MK / 8)) * 8;
+      if constexpr (SPLIT) {
+        const float f[8] = {xr[it][0].x, xr[it][0].y, xr[it][0].z, xr[it][0].w, xr[it][1].x, xr[it][1].y, xr[it][1].z, xr[it][1].w};
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          hi[e] = sm100::TypeTraits<T>::pack2(f[2 * e], f[2 * e + 1]);
+          const float2 back = sm100::TypeTraits<T>::unpack2(hi[e]);
+          lo[e] = sm100::TypeTraits<T>::pack2(f[2 * e] - back.x, f[2 * e + 1] - back.y);
+        }
+        *reinterpret_cast<uint4*>(&xs[0][j][k8]) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(&xs[SPLIT ? 1 : 0][j][k8]) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      } else {
+        *reinterpret_cast<uint4*>(&xs[0][j][k8]) = xr16[it];
+      }
+    }
+#pragma unroll
+    for (int it = 0; it < WI; ++it) {
+      const int idx = threadIdx.x + it * 128;
+      *reinterpret_cast<uint4*>(&ws[idx / 8][(idx & 7) * 8]) = wr[it];
+    }
+  };
+
+  __syncthreads();                               // the merge weights are in place
+  fetch(0);
+  for (int k0 = 0; k0 < in_dim; k0 += MK) {
+    if (k0 > 0) __syncthreads();                 // the previous chunk's MMAs have read their operands
+    stage();
     __syncthreads();
+    if (k0 + MK < in_dim) fetch(k0 + MK);
 #pragma unroll
     for (int kk = 0; kk < MK; kk += 16) {
       uint32_t a[SPLIT ? 2 : 1][4];
@@ -171,12 +240,11 @@ projection_mma_kernel(const TI* __restrict__ x, int64_t x_sb, int64_t x_sh, cons
   for (int n = 0; n < MN / 8; ++n) {
     const int c = c0 + n * 8 + 2 * t;
     if (c >= out_dim) continue;
+    // (c is even and the launcher has checked that rows start on 4-byte boundaries: one store per pair)
     T* o0 = out + (int64_t)r0 * o_sb + (int64_t)h * o_sh + c;
     T* o1 = out + (int64_t)(r0 + 8) * o_sb + (int64_t)h * o_sh + c;
-    const T v00 = sm100::TypeTraits<T>::from_f(acc[n][0]), v01 = sm100::TypeTraits<T>::from_f(acc[n][1]);
-    const T v10 = sm100::TypeTraits<T>::from_f(acc[n][2]), v11 = sm100::TypeTraits<T>::from_f(acc[n][3]);
-    if (r0 < batch) { o0[0] = v00; o0[1] = v01; }
-    if (r0 + 8 < batch) { o1[0] = v10; o1[1] = v11; }
+    if (r0 < batch) *reinterpret_cast<uint32_t*>(o0) = sm100::TypeTraits<T>::pack2(acc[n][0], acc[n][1]);
+    if (r0 + 8 < batch) *reinterpret_cast<uint32_t*>(o1) = sm100::TypeTraits<T>::pack2(acc[n][2], acc[n][3]);
   }
 }
 
@@ -215,17 +283,19 @@ static int absorb_batched(const xkv_decode_params& p, T* qeff, int dk, cudaStrea
   const int div = p.num_heads / p.k_proj_heads;
   // w[h/div, i = d, c = r] = k_proj[(h/div) * kp_sh + r * kp_sr + d * kp_sd]
   if (projection_mma_ok<T>(p.q, p.q_sb, p.q_sh, p.k_proj, p.kp_sh, p.kp_sd, p.kp_sr, p.head_dim, p.k_rank) && dk % 2 == 0 &&
-      (p.tail_dim == 0 || p.q_tail != nullptr)) {
+      (reinterpret_cast<uintptr_t>(qeff) & 3u) == 0 &&
+      (p.tail_dim == 0 || (p.q_tail != nullptr && p.tail_dim % 8 == 0 && dk % 8 == 0 && p.k_rank % 8 == 0 &&
+                           sm100::aligned16(p.q_tail) && p.qt_sb % 8 == 0 && p.qt_sh % 8 == 0 && sm100::aligned16(qeff)))) {
     const dim3 mgrid((unsigned)(p.k_rank / MN), (unsigned)p.num_heads, (unsigned)ceil_div(p.batch, MM));
     const T* tail = p.tail_dim > 0 ? static_cast<const T*>(p.q_tail) : nullptr;
     if (p.kp_sd == 1)
       projection_mma_kernel<T, T, true><<<mgrid, 128, 0, st>>>(static_cast<const T*>(p.q), p.q_sb, p.q_sh,
           static_cast<const T*>(p.k_proj), div, p.kp_sh, p.kp_sd, p.kp_sr, qeff, (int64_t)p.num_heads * dk, (int64_t)dk, p.batch,
-          p.head_dim, p.k_rank, tail, p.qt_sb, p.qt_sh, p.tail_dim, p.k_rank);
+          p.head_dim, p.k_rank, tail, p.qt_sb, p.qt_sh, p.tail_dim, p.k_rank, nullptr, 1);
     else
       projection_mma_kernel<T, T, false><<<mgrid, 128, 0, st>>>(static_cast<const T*>(p.q), p.q_sb, p.q_sh,
           static_cast<const T*>(p.k_proj), div, p.kp_sh, p.kp_sd, p.kp_sr, qeff, (int64_t)p.num_heads * dk, (int64_t)dk, p.batch,
-          p.head_dim, p.k_rank, tail, p.qt_sb, p.qt_sh, p.tail_dim, p.k_rank);
+          p.head_dim, p.k_rank, tail, p.qt_sb, p.qt_sh, p.tail_dim, p.k_rank, nullptr, 1);
     return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
   }
   const dim3 grid((unsigned)ceil_div(p.k_rank, NT), (unsigned)p.num_heads, (unsigned)ceil_div(p.batch, BC));
@@ -245,18 +315,31 @@ int launch_absorb_query_batched(const xkv_decode_params& p, void* qeff, int dk, 
 }
 
 // out[b, h, :] = o_lat[b, h, :] . v_proj[h / div] (fp32 merged latent rows -> output dtype), shared projection.
-int launch_value_projection_batched(const float* o_lat, const xkv_decode_params& p, cudaStream_t st) {
+static bool value_projection_mma_ok(const float* o_lat, const xkv_decode_params& p, int64_t l_sb, int64_t l_sh) {
+  return (p.dtype == XKV_BF16 || p.dtype == XKV_F16) && p.o_sb % 2 == 0 && p.o_sh % 2 == 0 &&
+         (reinterpret_cast<uintptr_t>(p.out) & 3u) == 0 &&
+         projection_mma_ok<float>(o_lat, l_sb, l_sh, p.v_proj, p.vp_sh, p.vp_sr, p.vp_sd, p.v_rank, p.value_dim);
+}
+
+bool value_projection_merges(const xkv_decode_params& p, int num_splits) {
+  if (num_splits < 1 || num_splits > MERGE_MAX || p.v_rank % 4 != 0) return false;
+  // (the partial rows sit in the 256-byte aligned workspace: only the matrix and the output decide)
+  return value_projection_mma_ok(nullptr, p, (int64_t)p.num_heads * num_splits * p.v_rank, (int64_t)num_splits * p.v_rank);
+}
+
+int launch_value_projection_batched(const float* o_lat, const xkv_decode_params& p, cudaStream_t st, const float* lse,
+                                    int num_splits) {
   const int div = p.num_heads / p.v_proj_heads;
+  if (num_splits > 1 && (lse == nullptr || !value_projection_merges(p, num_splits))) return XKV_ERR_UNSUPPORTED;
   const dim3 grid((unsigned)ceil_div(p.value_dim, NT), (unsigned)p.num_heads, (unsigned)ceil_div(p.batch, BC));
   const size_t smem = (size_t)BC * p.v_rank * sizeof(float);
-  const int64_t l_sb = (int64_t)p.num_heads * p.v_rank, l_sh = p.v_rank;
+  const int64_t l_sb = (int64_t)p.num_heads * num_splits * p.v_rank, l_sh = (int64_t)num_splits * p.v_rank;
   // w[h/div, i = r, c = d] = v_proj[(h/div) * vp_sh + r * vp_sr + d * vp_sd]
-  if ((p.dtype == XKV_BF16 || p.dtype == XKV_F16) && p.o_sb % 2 == 0 && p.o_sh % 2 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 3u) == 0 &&
-      projection_mma_ok<float>(o_lat, l_sb, l_sh, p.v_proj, p.vp_sh, p.vp_sr, p.vp_sd, p.v_rank, p.value_dim)) {
+  if (value_projection_mma_ok(o_lat, p, l_sb, l_sh)) {
     const dim3 mgrid((unsigned)(p.value_dim / MN), (unsigned)p.num_heads, (unsigned)ceil_div(p.batch, MM));
 #define XKV_VPM(T, WK)                                                                                                   \
   projection_mma_kernel<float, T, WK><<<mgrid, 128, 0, st>>>(o_lat, l_sb, l_sh, static_cast<const T*>(p.v_proj), div, p.vp_sh, \
-      p.vp_sr, p.vp_sd, static_cast<T*>(p.out), p.o_sb, p.o_sh, p.batch, p.v_rank, p.value_dim, nullptr, 0, 0, 0, 0)
+      p.vp_sr, p.vp_sd, static_cast<T*>(p.out), p.o_sb, p.o_sh, p.batch, p.v_rank, p.value_dim, nullptr, 0, 0, 0, 0, lse, num_splits)
     if (p.dtype == XKV_BF16) { if (p.vp_sr == 1) XKV_VPM(__nv_bfloat16, true); else XKV_VPM(__nv_bfloat16, false); }
     else { if (p.vp_sr == 1) XKV_VPM(__half, true); else XKV_VPM(__half, false); }
 #undef XKV_VPM

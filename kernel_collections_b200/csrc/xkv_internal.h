@@ -109,7 +109,11 @@ int launch_absorb_query_lowp(const xkv_decode_params& p, void* qeff, int dk, cud
 // projections batched over the batch rows, for matrices shared by the batch (projections.cu)
 bool batched_projection_fits(int batch, int in_dim);
 int launch_absorb_query_batched(const xkv_decode_params& p, void* qeff, int dk, cudaStream_t st);
-int launch_value_projection_batched(const float* o_lat, const xkv_decode_params& p, cudaStream_t st);
+// `lse` / `num_splits` > 1: o_lat holds per-split partial rows [batch][heads][splits][v_rank] with their log-sum-exps
+// [batch][heads][splits], merged while they are staged (value_projection_merges says whether this call can do that)
+int launch_value_projection_batched(const float* o_lat, const xkv_decode_params& p, cudaStream_t st,
+                                    const float* lse = nullptr, int num_splits = 1);
+bool value_projection_merges(const xkv_decode_params& p, int num_splits);
 
 // ---- shared-latent decode on tcgen05, two CTAs per tile (latent_pair_sm100.cu) -------------------
 bool latent_pair_supported(const xkv_decode_params& p);

@@ -92,12 +92,13 @@ def test_mla(dtype, case):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("k_major", [False, True])
-@pytest.mark.parametrize("case", [(5, 64, 256, 64, 300), (70, 128, 512, 64, 130), (16, 72, 128, 0, 90)])
+@pytest.mark.parametrize("case", [(5, 64, 256, 64, 300), (70, 128, 512, 64, 130), (16, 72, 128, 0, 90), (60, 128, 512, 64, 1280)])
 def test_mla_absorbed_with_batch_wide_projections(dtype, k_major, case):
     """W_uk folded into the queries and W_uv applied to the merged latent rows as tensor-core products over the
     whole batch (projection matrices shared by the batch, 4 rows or more): batches that do not fill a 64-row
     strip and ones that need two, head counts off the block size, and both memory orders of the matrices
-    (contraction index contiguous or output column contiguous), against the oracle."""
+    (contraction index contiguous or output column contiguous), against the oracle.  The batch of 5 is cut into
+    several KV splits per row, which the value projection merges while it stages the partial rows."""
     b, H, lora, rope, L = case
     g = torch.Generator().manual_seed(46)
     nope, vd = 128, 128
@@ -235,6 +236,26 @@ def test_cta_pair_kernel_against_oracle_and_mma_sync_kernel(dtype, case):
     close(got2, torch.matmul(torch.softmax((torch.matmul(q2.float(), c2.float().transpose(-1, -2))
                                             + (0 if qr is None else torch.matmul(qr.float(), kr.float().transpose(-1, -2)))) * 0.4, -1),
                              c2.float()[..., :Rv]), "latent_pair with climbing logits")
+
+
+def test_cta_pair_kernel_with_nearly_as_many_rows_as_pair_slots():
+    """60 rows on the GPU's 74 CTA-pair slots: one KV split per row, one wave."""
+    b, H, lora, rope, L = 60, 128, 512, 64, 1280
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(47)
+    qn = (torch.randn(b, H, lora, generator=g) / 3).to(dtype)
+    c = (torch.randn(b, L, lora, generator=g) / 3).to(dtype)
+    qr = (torch.randn(b, H, rope, generator=g) / 3).to(dtype)
+    kr = (torch.randn(b, L, rope, generator=g) / 3).to(dtype)
+    cd = c.to(DEV)
+    kw = dict(score_mode=_C.SCORE_LATENT, value_mode=_C.VALUE_LATENT, q=qn.to(DEV), k=cd, v=cd, q_tail=qr.to(DEV),
+              k_tail=kr.to(DEV), sm_scale=0.3, num_kv_heads=1)
+    assert ops.plan(**kw) == "latent_pair"
+    got = ops.decode(entry="xkv_mla_decode", **kw)
+    status_ok()
+    s = (torch.matmul(qn.float(), c.float().transpose(-1, -2)) + torch.matmul(qr.float(), kr.float().transpose(-1, -2))) * 0.3
+    close(got, torch.matmul(torch.softmax(s, -1), c.float()), "latent_pair with uneven splits")
+    assert torch.equal(got, ops.decode(entry="xkv_mla_decode", **kw))
 
 
 @pytest.mark.parametrize("case", [(2, 64, 256, 0, 900, 256), (1, 96, 256, 64, 400, 128)])
