@@ -74,7 +74,13 @@ struct Args {
   int batch, kv_len, num_heads, dk;
   int num_splits, tiles_per_row;
   float scale_log2;
-  const void* qeff;                       // [batch][H][dk], working dtype
+  const void* qeff;                       // [batch][H][dk], working dtype; null: the two parts are read where the caller has them
+  const void* q;                          // columns [0, q_cols) of a query row: q + b * q_sb + h * q_sh
+  const void* q_tail;                     // columns [q_cols, dk): q_tail + b * qt_sb + h * qt_sh
+  int64_t q_sb, q_sh, qt_sb, qt_sh;
+  int q_cols;
+  void* out;                              // not null (one split only): finished rows in the working dtype, out + b * o_sb + h * o_sh
+  int64_t o_sb, o_sh;
   float* partial_o;                       // [batch][H][splits][rv]
   float* lse;                             // [batch][H][splits]
   int rv;
@@ -212,7 +218,15 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         v[u] = make_uint4(0, 0, 0, 0);
         if (idx < nq) {
           const int qi = idx >> 10, r = (idx >> 3) & 127, ch = idx & 7;
-          if (h0 + r < a.num_heads) v[u] = *reinterpret_cast<const uint4*>(qg + (int64_t)r * a.dk + bl.qcol[bl.ks0 + qi] + ch * 8);
+          if (h0 + r < a.num_heads) {
+            const int col = bl.qcol[bl.ks0 + qi] + ch * 8;
+            if (a.qeff != nullptr)
+              v[u] = *reinterpret_cast<const uint4*>(qg + (int64_t)r * a.dk + col);
+            else if (col < a.q_cols)
+              v[u] = *reinterpret_cast<const uint4*>(static_cast<const T_*>(a.q) + (int64_t)b * a.q_sb + (int64_t)(h0 + r) * a.q_sh + col);
+            else
+              v[u] = *reinterpret_cast<const uint4*>(static_cast<const T_*>(a.q_tail) + (int64_t)b * a.qt_sb + (int64_t)(h0 + r) * a.qt_sh + (col - a.q_cols));
+          }
         }
       }
 #pragma unroll
@@ -517,7 +531,17 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 32; ++e) v[e] = 0u;
         }
-        if (live) {
+        if (live && a.out != nullptr) {
+          // the only split of its row: the normalised row is the result, stored in the working dtype
+          T_* orow = static_cast<T_*>(a.out) + (int64_t)b * a.o_sb + (int64_t)h * a.o_sh + col_out + c;
+#pragma unroll
+          for (int e = 0; e < 32; e += 8)
+            *reinterpret_cast<uint4*>(orow + e) =
+                make_uint4(TypeTraits<T_>::pack2(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv),
+                           TypeTraits<T_>::pack2(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv),
+                           TypeTraits<T_>::pack2(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv),
+                           TypeTraits<T_>::pack2(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv));
+        } else if (live) {
 #pragma unroll
           for (int e = 0; e < 32; e += 4)
             *reinterpret_cast<float4*>(po + c + e) =
@@ -762,17 +786,27 @@ int latent_pair_decode(const xkv_decode_params& p, const LatentTcPlan& pl, void*
   int* status = reinterpret_cast<int*>(w);
   sm100::clear_status_kernel<<<1, 64, 0, st>>>(status);
   void* qeff = w + pl.off_qeff;
+  // queries that need no projection are read where they are when every row piece is 16-byte aligned
+  const bool q_direct = p.k_proj == nullptr && aligned16(p.q) && p.q_sb % 8 == 0 && p.q_sh % 8 == 0 &&
+                        (p.tail_dim == 0 || (aligned16(p.q_tail) && p.qt_sb % 8 == 0 && p.qt_sh % 8 == 0));
   // a projection shared by the batch is folded into the queries one matrix strip at a time (each matrix
-  // element read once per 16 batch rows); per-batch projections go row by row
-  int rc = (p.k_proj && p.kp_sb == 0 && batched_projection_fits(p.batch, p.head_dim))
+  // element read once per strip of batch rows); per-batch projections go row by row
+  int rc = q_direct ? XKV_OK
+           : (p.k_proj && p.kp_sb == 0 && batched_projection_fits(p.batch, p.head_dim))
                ? launch_absorb_query_batched(p, qeff, dk, st)
                : launch_absorb_query_lowp(p, qeff, dk, st);
   if (rc != XKV_OK) return rc;
+  // one split per row, no value projection, no log-sum-exp wanted: the kernel stores the result itself
+  const bool out_direct = pl.num_splits == 1 && p.v_proj == nullptr && p.lse_out == nullptr && p.value_dim == p.v_rank &&
+                          aligned16(p.out) && p.o_sb % 8 == 0 && p.o_sh % 8 == 0;
   Args a;
+  a.q = p.q; a.q_tail = p.q_tail; a.q_sb = p.q_sb; a.q_sh = p.q_sh; a.qt_sb = p.qt_sb; a.qt_sh = p.qt_sh;
+  a.q_cols = p.k_rank;
+  a.out = out_direct ? p.out : nullptr; a.o_sb = p.o_sb; a.o_sh = p.o_sh;
   a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = p.num_heads; a.dk = dk;
   a.num_splits = pl.num_splits; a.tiles_per_row = pl.tiles;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
-  a.qeff = qeff;
+  a.qeff = q_direct ? nullptr : qeff;
   a.partial_o = reinterpret_cast<float*>(w + pl.off_partial);
   a.lse = reinterpret_cast<float*>(w + pl.off_lse);
   a.rv = p.v_rank;
@@ -783,6 +817,7 @@ int latent_pair_decode(const xkv_decode_params& p, const LatentTcPlan& pl, void*
   rc = p.dtype == XKV_BF16 ? launch<__nv_bfloat16>(tK, tKt, tV, a, head_blocks, st)
                            : launch<__half>(tK, tKt, tV, a, head_blocks, st);
   if (rc != XKV_OK) return rc;
+  if (out_direct) return XKV_OK;
   if (pl.off_olat != 0 && pl.num_splits == 1 && !p.lse_out)   // one split: its normalised partial IS the latent output
     return launch_value_projection_batched(a.partial_o, p, st);
   if (pl.off_olat != 0 && !p.lse_out && value_projection_merges(p, pl.num_splits))   // a few splits: merged as the projection stages them
