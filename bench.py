@@ -504,6 +504,9 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="batch rows per GPU (cut-down case for profiler captures)")
     ap.add_argument("--kv-len", type=int, default=0, help="context length override (cut-down case)")
     ap.add_argument("--pair", default="auto", choices=["auto", "on", "off"], help="key reconstruction: CTA-pair kernel")
+    ap.add_argument("--graph", default="off", choices=["off", "on"],
+                    help="N = 1: capture one step (all of its launches) in a CUDA graph after the warm-up and replay it in the "
+                         "timed region, as a serving loop would; the end-to-end figure stays the plain call")
     ap.add_argument("--gather", default="auto", choices=["auto", "nccl", "peer"],
                     help="N > 1: how the outputs are gathered.  peer = the library's peer-store kernel over symmetric memory; "
                          "auto = peer for steps under 2 ms when it can be set up and agrees with NCCL, else NCCL")
@@ -618,11 +621,25 @@ def main():
     for _ in range(warm):
         out = step()
     barrier()
+    run_step = step
+    if args.graph == "on" and world == 1:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_out = step()
+        torch.cuda.synchronize()
+
+        def run_step():
+            graph.replay()
+            return graph_out
+        for _ in range(3):
+            run_step()
+        barrier()
+        config["cuda_graph"] = "one step captured after the warm-up and replayed in the timed region"
     sampler = ClockSampler(local_rank)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     ev[0].record(stream)
     for i in range(args.steps):
-        out = step()
+        out = run_step()
         ev[i + 1].record(stream)
     barrier()
     clocks = sampler.stop()

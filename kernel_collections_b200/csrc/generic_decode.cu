@@ -534,11 +534,64 @@ int generic_decode_builtin_scratch(const xkv_decode_params& p, const GenericPlan
   return generic_decode(p, pl, ptr, st);
 }
 
+// The same merge without a value projection, one WARP per (batch, head) row and no block-wide barriers: every
+// lane walks the splits in order (same weights, same order of additions as merge_kernel, so the two agree bit for
+// bit) over its own 4-column groups, with 16-byte loads of the partial rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+merge_rows_kernel(const float* __restrict__ partial_o, const float* __restrict__ lse, T* __restrict__ out, int rows,
+                  int num_heads, int heads_total, int head_offset, int S, int Dacc, int64_t o_sb, int64_t o_sh,
+                  float* __restrict__ lse_out, int64_t lse_sb) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int b = row / num_heads, h = row - b * num_heads;
+  const int64_t prow = (int64_t)b * heads_total + head_offset + h;
+  const float* ls = lse + prow * S;
+  const float* po = partial_o + prow * S * (int64_t)Dacc;
+  float mx = -CUDART_INF_F;
+  for (int s = 0; s < S; ++s) mx = fmaxf(mx, ls[s]);
+  float tot = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const float v = ls[s];
+    tot += (v == -CUDART_INF_F) ? 0.f : expf(v - mx);
+  }
+  const float inv = tot > 0.f ? 1.f / tot : 0.f;
+  if (lane == 0 && lse_out) lse_out[(int64_t)b * lse_sb + h] = tot > 0.f ? mx + logf(tot) : -CUDART_INF_F;
+  T* orow = out + (int64_t)b * o_sb + (int64_t)h * o_sh;
+  for (int c = lane * 4; c < Dacc; c += 128) {
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < S; ++s) {
+      const float v = ls[s];
+      const float w = (v == -CUDART_INF_F) ? 0.f : expf(v - mx);
+      if (w != 0.f) {
+        const float4 p4 = *reinterpret_cast<const float4*>(po + (int64_t)s * Dacc + c);
+        o.x = fmaf(w, p4.x, o.x); o.y = fmaf(w, p4.y, o.y); o.z = fmaf(w, p4.z, o.z); o.w = fmaf(w, p4.w, o.w);
+      }
+    }
+    stf(orow + c, o.x * inv); stf(orow + c + 1, o.y * inv); stf(orow + c + 2, o.z * inv); stf(orow + c + 3, o.w * inv);
+  }
+}
+
 int launch_merge(const float* partial_o, const float* lse, void* out, int dtype, int batch, int num_heads,
                  int num_splits, int acc_dim, int value_dim, const void* v_proj, int v_proj_heads,
                  int64_t vp_sb, int64_t vp_sh, int64_t vp_sr, int64_t vp_sd, int64_t o_sb, int64_t o_sh,
                  cudaStream_t st, int heads_total, int head_offset, float* lse_out, int64_t lse_sb) {
   if (heads_total <= 0) heads_total = num_heads;
+  if (v_proj == nullptr && value_dim == acc_dim && acc_dim % 4 == 0 && (reinterpret_cast<uintptr_t>(partial_o) & 15u) == 0) {
+    const int rows = batch * num_heads;
+#define XKV_MERGE_ROWS(T)                                                                                         \
+  merge_rows_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(partial_o, lse, static_cast<T*>(out), rows, num_heads, \
+                                                                    heads_total, head_offset, num_splits, acc_dim, o_sb, o_sh, \
+                                                                    lse_out, lse_sb)
+    switch (dtype) {
+      case XKV_F32: XKV_MERGE_ROWS(float); break;
+      case XKV_BF16: XKV_MERGE_ROWS(__nv_bfloat16); break;
+      case XKV_F16: XKV_MERGE_ROWS(__half); break;
+      default: return XKV_ERR_BAD_ARG;
+    }
+#undef XKV_MERGE_ROWS
+    return cudaGetLastError() == cudaSuccess ? XKV_OK : XKV_ERR_LAUNCH;
+  }
   const size_t smem = (size_t)(num_splits + acc_dim) * sizeof(float);
   if (smem > 40 * 1024) return XKV_ERR_UNSUPPORTED;
   const dim3 grid(num_heads, batch);
