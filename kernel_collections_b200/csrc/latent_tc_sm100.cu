@@ -598,7 +598,11 @@ int latent_tc_decode(const xkv_decode_params& pin, const LatentTcPlan& pl, void*
   int* status = reinterpret_cast<int*>(w);
   clear_status_kernel<<<1, 64, 0, st>>>(status);
   void* qeff = w + pl.off_qeff;
-  if (launch_absorb_query_lowp(p, qeff, dk, st) != XKV_OK) return XKV_ERR_LAUNCH;
+  // a projection shared by the batch is folded into the queries as one tensor-core product over the batch rows
+  const int arc = (p.k_proj && p.kp_sb == 0 && batched_projection_fits(p.batch, p.head_dim))
+                      ? launch_absorb_query_batched(p, qeff, dk, st)
+                      : launch_absorb_query_lowp(p, qeff, dk, st);
+  if (arc != XKV_OK) return XKV_ERR_LAUNCH;
   Args a;
   a.batch = p.batch; a.kv_len = p.kv_len; a.num_heads = p.num_heads;
   a.dk = dk; a.rk = p.k_rank; a.rv = p.v_rank; a.alias_v = alias ? 1 : 0;
@@ -621,6 +625,9 @@ int latent_tc_decode(const xkv_decode_params& pin, const LatentTcPlan& pl, void*
                      ? dispatch<__nv_bfloat16, false>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st)
                      : dispatch<__half, false>(pl.heads_per_cta, nt, tK, tKt, tV, a, hblocks, pl.smem_bytes, st);
   if (rc != XKV_OK || lo) return rc;
+  // a shared value projection over a few splits: merged while the batch-wide product stages the partial rows
+  if (p.v_proj && p.vp_sb == 0 && p.batch >= 4 && !p.lse_out && value_projection_merges(p, pl.num_splits))
+    return launch_value_projection_batched(a.partial_o, p, st, a.lse, pl.num_splits);
   return launch_merge(a.partial_o, a.lse, p.out, p.dtype, p.batch, p.num_heads, pl.num_splits, p.v_rank, p.value_dim,
                       p.v_proj, p.v_proj ? p.v_proj_heads : 1, p.vp_sb, p.vp_sh, p.vp_sr, p.vp_sd, p.o_sb, p.o_sh, st, 0, 0,
                       p.lse_out, p.lse_sb);

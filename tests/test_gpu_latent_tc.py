@@ -56,6 +56,28 @@ def test_factorized_absorbed(dtype, case):
     close(o, O.xkv_fused(q[:, :, 0], Ak, Bk, Av, Bv, 0.07), "gqa_xKV_no_pe (latent_tc)")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", [(8, 32, 8, 128, 700, 256, 384), (5, 16, 4, 64, 257, 128, 128), (16, 32, 8, 128, 3000, 256, 256)])
+def test_factorized_absorbed_with_projections_shared_by_the_batch(dtype, case):
+    """B_k / B_v as model weights (one copy, stride 0 over the batch) and 4 or more rows: both projections run as
+    tensor-core products over the whole batch, the value one merging the KV splits as it stages them."""
+    b, H, KVH, D, L, Rk, Rv = case
+    g = torch.Generator().manual_seed(48)
+    q = torch.randn(b, H, 1, D, generator=g).to(dtype)
+    Ak = torch.randn(b, L, Rk, generator=g).to(dtype)
+    Bk = (torch.randn(1, KVH, Rk, D, generator=g) / Rk ** 0.5).to(dtype)
+    Av = torch.randn(b, L, Rv, generator=g).to(dtype)
+    Bv = (torch.randn(1, KVH, Rv, D, generator=g) / Rv ** 0.5).to(dtype)
+    qd, Akd, Avd = (x.to(DEV) for x in (q, Ak, Av))
+    Bkd, Bvd = Bk.to(DEV).expand(b, -1, -1, -1), Bv.to(DEV).expand(b, -1, -1, -1)
+    got = K.group_query_attention_factorized(qd, Akd, Bkd, Avd, Bvd)
+    status_ok()
+    close(got, O.gqa_factorized(q, Ak, Bk.expand(b, -1, -1, -1), Av, Bv.expand(b, -1, -1, -1)), "factorized, shared B, vs oracle")
+    per_row = K.group_query_attention_factorized(qd, Akd, Bkd.contiguous(), Avd, Bvd.contiguous())
+    close(got, per_row.float().cpu(), "shared B vs per-row B", 4e-3, 3e-3)
+    assert torch.equal(got, K.group_query_attention_factorized(qd, Akd, Bkd, Avd, Bvd))
+
+
 MLA = [  # b, H, lora, rope, L
     (2, 16, 128, 64, 203), (1, 128, 512, 64, 1500), (3, 64, 256, 64, 64), (1, 32, 512, 64, 4097),
 ]
