@@ -152,7 +152,7 @@ def test_rope_query_matches_oracle():
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_shared_B_matrix_and_strided_views(dtype):
-    """BASELINE-style shared B (R, KVH*D) broadcast over the batch, and non-contiguous K/V views."""
+    """Shared B as in the benchmark configurations (R, KVH*D) broadcast over the batch, and non-contiguous K/V views."""
     b, H, KVH, D, L, R, theta = 3, 8, 2, 64, 75, 32, 500000.0
     gen = g(5)
     q, qd = mk((b, H, 1, D), dtype, gen=gen)
