@@ -178,12 +178,25 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap tmV, const Args a) {
         dst[i] = (live && tile < tile_end && tk < row_len) ? __ldg(lrow + tk) * LOG2E : -CUDART_INF_F;
       }
     };
+    // The register loads run one tile ahead, which covers an L2 hit but not a trip to HBM: the row's 256 bytes of
+    // the tile three ahead are asked into L2 meanwhile (two 128-byte lines; a hint, so a line past the row is harmless
+    // as long as it lies inside the logits buffer, which the tile_end test guarantees).
+    auto prefetch_l2 = [&](int tile) {
+      if (live && tile < tile_end && (tile + 1) * TK <= row_len) {
+        const float* pf = lrow + (int64_t)tile * TK;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pf));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pf + 32));
+      }
+    };
+    prefetch_l2(tile_begin + 1);
+    prefetch_l2(tile_begin + 2);
     fetch(tile_begin, nxt);
     int pbuf = 0;
     uint32_t pph = 0;
     for (int tile = tile_begin; tile < tile_end; ++tile) {
 #pragma unroll
       for (int i = 0; i < TK; ++i) cur[i] = nxt[i];
+      prefetch_l2(tile + 3);
       fetch(tile + 1, nxt);
       float tmax = -CUDART_INF_F;
 #pragma unroll
@@ -191,24 +204,21 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap tmV, const Args a) {
       // does this row's reference have to move?  (first finite tile, or the tile tops it by > 8)
       const bool move = tmax > m_ref + RESCALE_THRESHOLD || (m_ref == -CUDART_INF_F && tmax > -CUDART_INF_F);
       // all 128 rows agree on whether to rescale (barrier with reduction), so the TMEM pass is uniform
-      uint32_t any;
-      {
-        const uint32_t mine = (move ? 1u : 0u) | (*abort_flag ? 2u : 0u);
-        uint32_t anym, anya;
+      // (one barrier per tile: a raised abort flag rides on the same vote and is told apart by a second, rare one)
+      auto vote = [](uint32_t mine) -> uint32_t {
+        uint32_t res;
         asm volatile(
             "{\n\t.reg .pred p, q;\n\t"
-            "setp.ne.u32 p, %2, 0;\n\t"
+            "setp.ne.u32 p, %1, 0;\n\t"
             "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
-            "selp.u32 %0, 1, 0, q;\n\t"
-            "setp.ne.u32 p, %3, 0;\n\t"
-            "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
-            "selp.u32 %1, 1, 0, q;\n\t}"
-            : "=r"(anym), "=r"(anya)
-            : "r"(mine & 1u), "r"(mine & 2u)
+            "selp.u32 %0, 1, 0, q;\n\t}"
+            : "=r"(res)
+            : "r"(mine)
             : "memory");
-        if (anya) break;
-        any = anym;
-      }
+        return res;
+      };
+      const uint32_t any = vote((move || *abort_flag) ? 1u : 0u);
+      if (any && vote(*abort_flag ? 1u : 0u)) break;
       if (any) {
         const float m_new = move ? tmax : m_ref;
         const float alpha = (m_ref == -CUDART_INF_F) ? 0.f : exp2f(m_ref - m_new);
@@ -256,10 +266,9 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap tmV, const Args a) {
         uint32_t pk[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float p0 = exp2f(cur[c8 * 8 + 2 * i] - mref), p1 = exp2f(cur[c8 * 8 + 2 * i + 1] - mref);
-          T q0 = TypeTraits<T>::from_f(p0), q1 = TypeTraits<T>::from_f(p1);
-          l_sum += TypeTraits<T>::to_f(q0) + TypeTraits<T>::to_f(q1);
-          pk[i] = (uint32_t)(*reinterpret_cast<uint16_t*>(&q0)) | ((uint32_t)(*reinterpret_cast<uint16_t*>(&q1)) << 16);
+          pk[i] = TypeTraits<T>::pack2(exp2f(cur[c8 * 8 + 2 * i] - mref), exp2f(cur[c8 * 8 + 2 * i + 1] - mref));
+          const float2 q = TypeTraits<T>::unpack2(pk[i]);
+          l_sum += q.x + q.y;
         }
         *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
