@@ -141,19 +141,38 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
+    // FL: this warp's 16 tokens x the 16 padded head rows of a tile, in the accumulator layout of S, loaded one
+    // tile ahead (the loads of tile + 1 are in flight while tile is worked on; token pairs as 8-byte loads when the
+    // rows allow it)
+    float sc_next[2][4];
+    const bool lg_pairs = FL && a.lg_sb % 2 == 0 && a.lg_sh % 2 == 0 && (reinterpret_cast<uintptr_t>(a.logits) & 7u) == 0;
+    auto load_logits = [&](int tile, float (&dst)[2][4]) {
+      const int tokb = tile * TILE + cw * 16 + 2 * t;
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int jr = 0; jr < 2; ++jr) {
+          const int row = g + jr * 8, tok = tokb + n * 8;
+          const float* src = a.logits + (int64_t)b * a.lg_sb + (int64_t)(kvh * G + row) * a.lg_sh + tok;
+          if (row < G && lg_pairs && tok + 1 < row_len) {
+            const float2 v = __ldg(reinterpret_cast<const float2*>(src));
+            dst[n][2 * jr] = v.x;
+            dst[n][2 * jr + 1] = v.y;
+          } else {
+            dst[n][2 * jr] = (row < G && tok < row_len) ? __ldg(src) : 0.f;
+            dst[n][2 * jr + 1] = (row < G && tok + 1 < row_len) ? __ldg(src + 1) : 0.f;
+          }
+        }
+    };
+    if (FL && tile_begin < tile_end) load_logits(tile_begin, sc_next);
     for (int tile = tile_begin; tile < tile_end && alive; ++tile) {
       float sc[2][4];
       if (FL) {
-        // this warp's 16 tokens x the 16 padded head rows, in the accumulator layout of S
-        const int tokb = tile * TILE + cw * 16 + 2 * t;
 #pragma unroll
         for (int n = 0; n < 2; ++n)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int row = g + (j >> 1) * 8, tok = tokb + n * 8 + (j & 1);
-            sc[n][j] = (row < G && tok < row_len)
-                           ? __ldg(a.logits + (int64_t)b * a.lg_sb + (int64_t)(kvh * G + row) * a.lg_sh + tok) : 0.f;
-          }
+          for (int j = 0; j < 4; ++j) sc[n][j] = sc_next[n][j];
+        if (tile + 1 < tile_end) load_logits(tile + 1, sc_next);
       }
       bool ok = mbar_wait(bar_full(stage), phase, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) {
