@@ -34,14 +34,21 @@ namespace {
 constexpr int T = 32;                        // tokens per tile
 constexpr int MAXB = 5;                      // 64-column blocks per CTA and tile
 constexpr int BLK = T * 128;                 // bytes of one [32 tokens x 64 columns] block
-constexpr int STAGES = 4;
+#ifndef XKV_LP_TMEM_P
+#define XKV_LP_TMEM_P 1
+#endif
+// The probabilities P of a tile are the A operand of O += P . V.  Kept in TENSOR memory (written with tcgen05.st by
+// the softmax threads, read by the MMA as its tensor-memory operand) they need no shared memory and no proxy fence,
+// and the 16 KB they would take there pay for a fifth ring stage.  (0: P through shared memory, four stages.)
+constexpr bool kTmemP = XKV_LP_TMEM_P != 0;
+constexpr int STAGES = kTmemP ? 5 : 4;
 constexpr int QBLK = 128 * 128;              // bytes of one [128 heads x 64 columns] query block
 constexpr int NTHREADS = 384;
 constexpr int TH = T / 2;                     // tokens per softmax thread (two threads share a head row)
 constexpr int OFF_Q = 0;
 constexpr int OFF_RING = OFF_Q + MAXB * QBLK;                 // 81920
 constexpr int OFF_P = OFF_RING + STAGES * MAXB * BLK;
-constexpr int P_BYTES = 128 * 128;                            // 128 head rows x 64 token slots (32 used)
+constexpr int P_BYTES = kTmemP ? 0 : 128 * 128;               // 128 head rows x 128 bytes: two buffers of 32 tokens
 constexpr int OFF_X = OFF_P + P_BYTES;                        // partial scores from the peer
 constexpr int X_BYTES = (T / 4) * 128 * 16;                   // [T/4][128 rows][4 floats] = 16384
 constexpr int XW_BYTES = X_BYTES / 8;                         // one softmax warp's share of an exchange buffer
@@ -54,6 +61,8 @@ static_assert(OFF_RING % 1024 == 0 && BLK % 1024 == 0 && OFF_P % 1024 == 0, "swi
 constexpr float RESCALE_THRESHOLD = 8.f;
 constexpr uint32_t S_COL0 = 256;             // tensor-memory columns: O in 0..255, three score buffers of 32 from 256
 constexpr int SBUF = 3;
+constexpr uint32_t P_COL0 = S_COL0 + SBUF * T;   // two P buffers of T / 2 columns (two 16-bit values per column)
+static_assert(P_COL0 + T <= 512, "tensor memory: O, score buffers, P buffers");
 #ifndef XKV_LP_SPLIT_ODD
 #define XKV_LP_SPLIT_ODD 0
 #endif
@@ -179,14 +188,16 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const uint32_t stage_bytes = (uint32_t)bl.n * BLK;
 
   const uint32_t bar0 = base + OFF_BAR;
-  auto bar_full = [&](int s) { return bar0 + 8u * s; };               // [4] a tile's blocks have landed
-  auto bar_empty = [&](int s) { return bar0 + 8u * (4 + s); };        // [4] P.V of the tile that used the stage has run
-  auto bar_sfull = [&](int i) { return bar0 + 8u * (8 + i); };        // [3] a score buffer holds S of a tile
-  auto bar_sempty = [&](int i) { return bar0 + 8u * (11 + i); };      // [3] the softmax threads have read it
-  auto bar_pfull = [&](int i) { return bar0 + 8u * (14 + i); };       // [2] a P buffer holds the probabilities of a tile
-  auto bar_pempty = [&](int i) { return bar0 + 8u * (16 + i); };      // [2] P.V of the tile that used it has run
-  const uint32_t bar_odone = bar0 + 8u * 18;
-  auto bar_xfull = [&](int i) { return bar0 + 8u * (19 + i); };       // [2] the peer's partial scores have landed in exchange buffer i
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };                       // [STAGES] a tile's blocks have landed
+  auto bar_empty = [&](int s) { return bar0 + 8u * (STAGES + s); };           // [STAGES] P.V of the tile that used the stage has run
+  auto bar_sfull = [&](int i) { return bar0 + 8u * (2 * STAGES + i); };       // [SBUF] a score buffer holds S of a tile
+  auto bar_sempty = [&](int i) { return bar0 + 8u * (2 * STAGES + SBUF + i); };   // [SBUF] the softmax threads have read it
+  constexpr int kBarP = 2 * STAGES + 2 * SBUF;
+  auto bar_pfull = [&](int i) { return bar0 + 8u * (kBarP + i); };            // [2] a P buffer holds the probabilities of a tile
+  auto bar_pempty = [&](int i) { return bar0 + 8u * (kBarP + 2 + i); };       // [2] P.V of the tile that used it has run
+  const uint32_t bar_odone = bar0 + 8u * (kBarP + 4);
+  auto bar_xfull = [&](int i) { return bar0 + 8u * (kBarP + 5 + i); };        // [2] the peer's partial scores have landed in exchange buffer i
+  static_assert(kBarP + 7 <= 24, "barrier slots");
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 4);
 
@@ -281,6 +292,7 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       // operand descriptors built once; the loops only add offsets
       const uint64_t dq0 = smem_desc(base + OFF_Q, 16, 1024), dk0 = smem_desc(base + OFF_RING, 16, 1024);
       const uint64_t dp0 = smem_desc(base + OFF_P, 16, 1024), dv0 = smem_desc(base + OFF_RING, BLK, 1024);
+      (void)dp0;
       // One thread issues every MMA, and what it spends per instruction on addresses and loop control is time the
       // tensor core idles (a 128 x 32 x 16 MMA takes 46 cycles): the usual step sets are compiled in, fully
       // unrolled with constant offsets; any other set runs the loop at the end.
@@ -322,10 +334,17 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           if (!XKV_LP_WAIT(3, true, mbar_wait(bar_pfull(i & 1), (uint32_t)(i >> 1) & 1u, abort_flag))) { ok = false; break; }
           tc_fence_after();
           const uint64_t dv_st = desc_advance(dv0, (uint32_t)((i % STAGES) * (MAXB * BLK)));
-          const uint64_t dp_i = desc_advance(dp0, (uint32_t)((i & 1) * 64));       // the two P buffers are the halves of the 128-byte rows
+          if constexpr (kTmemP) {
+            const uint32_t tp = tmem_base + P_COL0 + (uint32_t)((i & 1) * (T / 2));
 #pragma unroll
-          for (int k4 = 0; k4 < T / 16; ++k4)
-            tc_mma(tmem_base, desc_advance(dp_i, k4 * 32), desc_advance(dv_st, k4 * 2048), idesc_o, (i == 0 && k4 == 0) ? 0u : 1u);
+            for (int k4 = 0; k4 < T / 16; ++k4)
+              tc_mma_ts(tmem_base, tp + (uint32_t)(k4 * 8), desc_advance(dv_st, k4 * 2048), idesc_o, (i == 0 && k4 == 0) ? 0u : 1u);
+          } else {
+            const uint64_t dp_i = desc_advance(dp0, (uint32_t)((i & 1) * 64));     // the two P buffers are the halves of the 128-byte rows
+#pragma unroll
+            for (int k4 = 0; k4 < T / 16; ++k4)
+              tc_mma(tmem_base, desc_advance(dp_i, k4 * 32), desc_advance(dv_st, k4 * 2048), idesc_o, (i == 0 && k4 == 0) ? 0u : 1u);
+          }
           tc_commit(bar_empty(i % STAGES));      // the tile's blocks and ...
           tc_commit(bar_pempty(i & 1));          // ... its P buffer are free once these MMAs have run
         }
@@ -472,19 +491,32 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         m_ref = m_new;
       }
       XKV_LP_MARK(15);
-      // ---- P row -> shared memory (K-major, 128-byte swizzle), row sum of the rounded values ------------
+      // ---- P row -> tensor memory (or shared memory, K-major with 128-byte swizzle), row sum of the rounded values
       const float mref = m_ref == -CUDART_INF_F ? 0.f : m_ref;
-      uint8_t* prow = sm + OFF_P + r * 128;
+      if constexpr (kTmemP) {
+        // lane = head row; a 32-bit column holds two consecutive tokens, this thread's 16 tokens are 8 columns
+        uint32_t pk[TH / 2];
 #pragma unroll
-      for (int c8 = 0; c8 < TH / 8; ++c8) {
-        uint32_t pk[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          pk[e] = TypeTraits<T_>::pack2(ex2_approx(s[c8 * 8 + 2 * e] - mref), ex2_approx(s[c8 * 8 + 2 * e + 1] - mref));
+        for (int e = 0; e < TH / 2; ++e) {
+          pk[e] = TypeTraits<T_>::pack2(ex2_approx(s[2 * e] - mref), ex2_approx(s[2 * e + 1] - mref));
           const float2 q = TypeTraits<T_>::unpack2(pk[e]);
           l_sum += q.x + q.y;
         }
-        *reinterpret_cast<uint4*>(prow + ((((i & 1) * 4 + half * (TH / 8) + c8) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        static_assert(TH == 16, "eight packed columns per thread");
+        tmem_st8(lane_addr + P_COL0 + (uint32_t)((i & 1) * (T / 2) + half * (TH / 2)), pk);
+      } else {
+        uint8_t* prow = sm + OFF_P + r * 128;
+#pragma unroll
+        for (int c8 = 0; c8 < TH / 8; ++c8) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            pk[e] = TypeTraits<T_>::pack2(ex2_approx(s[c8 * 8 + 2 * e] - mref), ex2_approx(s[c8 * 8 + 2 * e + 1] - mref));
+            const float2 q = TypeTraits<T_>::unpack2(pk[e]);
+            l_sum += q.x + q.y;
+          }
+          *reinterpret_cast<uint4*>(prow + ((((i & 1) * 4 + half * (TH / 8) + c8) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
       }
       // ragged batch, last tile of the row: value rows past the row's own length may hold anything (NaN
       // included, and 0 * NaN is NaN): zero them before the MMAs read the tile
@@ -500,7 +532,14 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         }
       }
       XKV_LP_MARK(16);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+      if constexpr (kTmemP) {
+        // only the zeroed tail rows above are generic writes that the tensor core reads through the async proxy
+        if (a.kv_lens != nullptr && tile0 + T > row_len) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tmem_wait_st();
+        tc_fence_before();
+      } else {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+      }
       mbar_arrive(bar_pfull(i & 1));
       XKV_LP_MARK(17);
     }
