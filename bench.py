@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Decode-attention benchmark.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--graph on] [--gather MODE]
 
 Default workload `c5`: the long-context sweep the headline metric is quoted on — factorized-K + RoPE
 GQA decode with dense V, 64 query / 8 KV heads, head_dim 128, rank 1024, context 131072, bf16, GLOBAL
@@ -16,6 +16,11 @@ launching stream, max over ranks); `e2e` is the same call through the public Pyt
 input copied from pinned host memory and the output read back inside the timed region; `parity` is the
 error of sampled batch rows of the very tensors that were timed against the CPU oracle; `cpu_baseline`
 is that oracle's own speed on the host cores (N = 1 only).
+
+--graph on (N = 1) replays one captured step from a CUDA graph in the timed region (the plain call leaves
+the GPU idle between the three to five launches of a sub-millisecond step); --gather nccl|peer|auto picks
+how the outputs are gathered at N > 1 (auto: the library's peer-store kernel for steps under 2 ms when
+symmetric memory is available and it agrees with NCCL, else NCCL).
 
 --impl reference times the reference's eager CPU math (the oracle port: the reference is Python that
 does not exist on the GPU box) on the host cores, one batch row at full context per step.
