@@ -516,3 +516,67 @@ def test_several_query_tokens_v2(dtype):
         q4 = torch.zeros(b, H * 4, D, dtype=dtype, device=DEV)
         assert ops.plan(score_mode=_C.SCORE_DENSE, value_mode=_C.VALUE_DENSE, q=q4, k=kd.transpose(1, 2), v=vd.transpose(1, 2),
                         sm_scale=1.0) == "dense_tc"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("case", [(3, 32, 16, 128), (2, 5, 3, 512), (1, 7, 1, 64)])
+def test_merge_warp_kernel_agrees_with_block_kernel_bit_for_bit(dtype, case):
+    """xkv_merge without a value projection runs one warp per row when the partial rows are 16-byte aligned and the
+    block-per-row kernel otherwise: same weights, same order of additions, so the two give the same bits.  The
+    misaligned copy of the same partials (shifted by one float inside a larger buffer) takes the block kernel.
+    Also against the plain formula."""
+    b, H, S, dim = case
+    g = torch.Generator(device="cuda").manual_seed(5)
+    part = torch.randn(b, H, S, dim, generator=g, device="cuda")
+    lse = torch.randn(b, H, S, generator=g, device="cuda") * 3
+    if S > 2:
+        lse[:, :, 1] = float("-inf")                       # an empty split drops out
+    lib = _C.load()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def run(p):
+        out = torch.empty(b, H, dim, dtype=dtype, device="cuda")
+        rc = lib.xkv_merge(p.data_ptr(), lse.data_ptr(), out.data_ptr(), _C.dtype_code(out), b, H, S, dim,
+                           out.stride(0), out.stride(1), stream)
+        _C.check(rc, "xkv_merge")
+        return out
+
+    aligned = run(part)
+    buf = torch.empty(part.numel() + 1, device="cuda")
+    shifted = buf[1:].view_as(part)
+    shifted.copy_(part)
+    assert shifted.data_ptr() % 16 != 0 and part.data_ptr() % 16 == 0
+    assert torch.equal(aligned, run(shifted))
+    w = torch.softmax(lse.double(), dim=-1)
+    want = (w.unsqueeze(-1) * part.double()).sum(2)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert (aligned.double() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+
+
+def test_decode_call_replays_from_a_cuda_graph():
+    """A decode call allocates nothing, reads no status and launches a fixed sequence of kernels, so it can be
+    captured in a CUDA graph after one eager warm-up call and replayed: the replay works on the tensors' CURRENT
+    contents (new queries written into the same buffers) and matches the eager call bit for bit."""
+    b, H, KVH, L, D, R = 4, 32, 8, 1024, 128, 256
+    g = torch.Generator(device="cuda").manual_seed(9)
+    q = torch.randn(b, H, 1, D, generator=g, device="cuda").bfloat16()
+    A = torch.randn(b, L, R, generator=g, device="cuda").bfloat16()
+    B = (torch.randn(R, KVH * D, generator=g, device="cuda") / R ** 0.5).bfloat16()
+    V = torch.randn(b, KVH, L, D, generator=g, device="cuda").bfloat16()
+    f = lambda: K.recon_rope_decode(q, A, B, V, theta=5e5)
+    f()                                              # eager warm-up: per-device look-ups happen here
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        f()                                          # the workspace of the capture stream exists before capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = f()
+    q.copy_(torch.randn(b, H, 1, D, generator=g, device="cuda").bfloat16())     # a new step's queries, same buffer
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, f())
+    rc, detail = _C.last_status(torch.device("cuda"))
+    assert rc == 0, detail
