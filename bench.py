@@ -773,7 +773,7 @@ def main():
                      "time at N > 1) charged to the dominant kernel"}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": wl.scaling, "vs_baseline": None, "dtype": str(wl.dtype).replace("torch.", ""),
+            "scaling": wl.scaling, "vs_baseline": None, "dtype": {"bfloat16": "bf16", "float16": "f16", "float32": "f32"}.get(str(wl.dtype).replace("torch.", ""), str(wl.dtype)),
             "data": "synthetic", "config": config, "clocks": clocks, "e2e": e2e,
             "gpu_launches": wl.launches * args.steps, "roofline": roof}
     if world > 1:
