@@ -28,7 +28,8 @@ NVCC_FLAGS = [
 
 
 def sources():
-    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC)
+                  if f.endswith(".cu") and os.path.isfile(os.path.join(CSRC, f)))
 
 
 def _headers():
@@ -67,7 +68,8 @@ def build(force: bool = False, verbose: bool = False, defines=(), lib_path: str 
     if not force and not defines and not overrides and not needs_build():
         return lib_path
     nvcc = find_nvcc()
-    obj_dir = OBJ_DIR if not (defines or overrides) else OBJ_DIR + "_" + "_".join(list(defines) + sorted(overrides))
+    tag = "_".join(list(defines) + sorted(overrides)).replace(".", "_").replace("=", "_")
+    obj_dir = OBJ_DIR if not (defines or overrides) else OBJ_DIR + "_" + tag
     os.makedirs(obj_dir, exist_ok=True)
     base = [nvcc, *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC] + [f"-D{d}" for d in defines]
     if verbose:
