@@ -494,6 +494,7 @@ latent_pair_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       // ---- P row -> tensor memory (or shared memory, K-major with 128-byte swizzle), row sum of the rounded values
       const float mref = m_ref == -CUDART_INF_F ? 0.f : m_ref;
       if constexpr (kTmemP) {
+        tc_fence_after();     // the P buffer was released through an mbarrier (tcgen05.commit of the MMAs that read it)
         // lane = head row; a 32-bit column holds two consecutive tokens, this thread's 16 tokens are 8 columns
         uint32_t pk[TH / 2];
 #pragma unroll
